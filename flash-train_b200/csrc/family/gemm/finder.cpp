@@ -1,0 +1,51 @@
+#include "family/gemm/finder.hpp"
+
+#include "ftcuda/ftcuda.h"
+#include "primitive/cuda/gemm/cuda_gemm.hpp"
+
+namespace ftrain {
+namespace {
+
+std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y; }
+
+}  // namespace
+
+// Regime map on B200 (148 SMs; the count is queried, not assumed):
+//   * very few rows of A (m <= 16): B is streamed exactly once, the problem is
+//     HBM-bound -> the skinny kernel first.
+//   * enough rows/columns to fill 128x256 tensor-core tiles: 3xTF32 on tcgen05.
+//     If those tiles cover less than half of the SMs while K is long, the
+//     split-K variant (workspace needed) goes first so the idle SMs take
+//     K-slices; the unsplit kernels follow for callers without workspace.
+//   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
+//     leave most SMs idle and K is long.
+// Every list ends with "Fp32Gemm", which needs no workspace and accepts every
+// layout, so a caller walking the Plan by workspace budget always finds a
+// runnable index.
+std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& problem, const Constraints& constraints) {
+    const GemmShape shape = problem.getShape();
+    std::int32_t sms      = 148;
+    if (ftcuda_device_sm_count(constraints.getDeviceId(), &sms, nullptr, 0) != 0 || sms <= 0) { sms = 148; }
+    const std::uint64_t sm_count = static_cast<std::uint64_t>(sms);
+
+    const char* simt         = cudaGemmName(FTCUDA_GEMM_SIMT);
+    const char* tensor       = cudaGemmName(FTCUDA_GEMM_TF32X3);
+    const char* tensor_split = cudaGemmName(FTCUDA_GEMM_TF32X3_SPLITK);
+    const char* skinny       = cudaGemmName(FTCUDA_GEMM_SKINNY);
+    const char* simt_split   = cudaGemmName(FTCUDA_GEMM_SIMT_SPLITK);
+
+    if (shape.m * shape.n == 0) { return {simt}; }
+    if (shape.m <= 16 && shape.k >= 256) { return {skinny, simt}; }
+
+    const bool fills_tensor_tiles = shape.m >= 128 && shape.n >= 128 && shape.k >= 256;
+    if (fills_tensor_tiles) {
+        const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 256);
+        if (tiles * 2 <= sm_count && shape.k >= 4096) { return {tensor_split, tensor, simt_split, simt}; }
+        return {tensor, simt};
+    }
+    const std::uint64_t simt_tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 128);
+    if (simt_tiles * 2 <= sm_count && shape.k >= 2048) { return {simt_split, simt}; }
+    return {simt};
+}
+
+}  // namespace ftrain

@@ -1,0 +1,116 @@
+/*
+ * ftcuda/ftcuda.h -- thin C ABI between the host pipeline and the CUDA
+ * (sm_100a) platform subtree.
+ *
+ * Everything the C++ host layers (family, primitives, plan) need from the GPU
+ * goes through these entry points: plain pointers, integers and fixed-size
+ * structs, integer return codes, no C++ types, no exceptions. The platform
+ * subtree behind it replaces the reference's HIP subtree:
+ *   ftcuda_current_device   <- getCurrentDeviceId / hipGetDevice
+ *                              (src/constraints.cpp:15-26)
+ *   ftcuda_gemm_supports    <- the platform half of Fp32Gemm::isApplicable
+ *                              (src/primitive/hygon/gemm/fp32_gemm.cpp:27-62)
+ *   ftcuda_gemm_configure   <- Fp32Gemm::configure (fp32_gemm.cpp:66-77)
+ *   ftcuda_gemm_launch      <- launchFp32Gemm (src/primitive/hygon/gemm/fp32_gemm.hip:35-51)
+ *   ftcuda_trace_push/pop   <- roctxRangePushA/Pop (src/trace.cpp:14-28)
+ *
+ * Return code: 0 = success; nonzero = failure with a NUL-terminated reason
+ * written to the caller's message buffer (when one is given).
+ */
+#ifndef FTCUDA_FTCUDA_H_
+#define FTCUDA_FTCUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__) || defined(__clang__)
+#    define FTCUDA_API __attribute__((visibility("default")))
+#else
+#    define FTCUDA_API
+#endif
+
+/* Kernel families. Each id is one Primitive of the GEMM family. */
+enum {
+    /* Exact FP32: SIMT FFMA tiles, TMA-staged when the layout allows it, with a
+     * predicated path for any strides. No workspace. */
+    FTCUDA_GEMM_SIMT = 0,
+    /* 3xTF32 split-precision on tcgen05 tensor cores with TMEM accumulators. */
+    FTCUDA_GEMM_TF32X3 = 1,
+    /* 3xTF32 with the K range split across CTAs; partial tiles go to the
+     * workspace and a second kernel reduces them and applies alpha/beta. */
+    FTCUDA_GEMM_TF32X3_SPLITK = 2,
+    /* Exact FP32 for very few rows of A: streams B once at HBM rate. */
+    FTCUDA_GEMM_SKINNY = 3,
+    /* Exact FP32 SIMT with the K range split across CTAs (workspace). */
+    FTCUDA_GEMM_SIMT_SPLITK = 4,
+    FTCUDA_GEMM_KERNEL_COUNT = 5,
+};
+
+/* One GEMM D = alpha * A * B + beta * C in terms of raw memory. Strides are in
+ * elements. c may be NULL (no beta * C term). c == d (in place) is allowed. */
+typedef struct {
+    const float* a;
+    const float* b;
+    const float* c;
+    float* d;
+    float alpha;
+    float beta;
+    uint64_t m;
+    uint64_t n;
+    uint64_t k;
+    int64_t a_row_stride, a_col_stride;
+    int64_t b_row_stride, b_col_stride;
+    int64_t c_row_stride, c_col_stride;
+    int64_t d_row_stride, d_col_stride;
+    int32_t device;
+} FtcudaGemmDesc;
+
+/* A configured launch: kernel choice, grid, pre-encoded TMA descriptors and
+ * kernel arguments. Opaque to the host code, trivially copyable, 64-byte
+ * aligned (a CUtensorMap inside needs that). */
+typedef struct {
+    uint64_t words[160];
+} __attribute__((aligned(64))) FtcudaGemmLaunch;
+
+/* Calling thread's current CUDA device. */
+FTCUDA_API int ftcuda_current_device(int32_t* device, char* message, size_t message_capacity);
+
+/* Number of SMs of a device (cached per device after the first query). */
+FTCUDA_API int ftcuda_device_sm_count(int32_t device, int32_t* sm_count, char* message, size_t message_capacity);
+
+/* 0 when kernel family `kernel` can run `desc`; otherwise nonzero and a reason.
+ * Pure host arithmetic on the descriptor: needs no device. */
+FTCUDA_API int ftcuda_gemm_supports(int kernel, const FtcudaGemmDesc* desc, char* message, size_t message_capacity);
+
+/* Fills `launch` for `kernel` on desc->device (tile shape, grid, TMA
+ * descriptors). Needs no device work beyond attribute queries. */
+FTCUDA_API int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, FtcudaGemmLaunch* launch, char* message,
+                                     size_t message_capacity);
+
+/* Workspace a configured launch needs, in bytes. */
+FTCUDA_API uint64_t ftcuda_gemm_workspace_bytes(const FtcudaGemmLaunch* launch);
+
+/* Enqueues the configured launch on `stream` (a cudaStream_t) and returns
+ * without synchronising. No allocation, no descriptor encoding. */
+FTCUDA_API int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                  void* stream, char* message, size_t message_capacity);
+
+/* Number of device kernels ftcuda_gemm_launch has enqueued from this process;
+ * benchmarks read it to report how many launches a timed region made. */
+FTCUDA_API uint64_t ftcuda_launch_count(void);
+
+/* NVTX range on the calling thread; push returns nonzero when a range was
+ * opened (pop only then). */
+FTCUDA_API int ftcuda_trace_push(const char* name);
+FTCUDA_API void ftcuda_trace_pop(void);
+FTCUDA_API void ftcuda_trace_mark(const char* name);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif
