@@ -1,0 +1,379 @@
+"""Benchmark of the FP32 GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0). A "step" is one execution of the Plan's
+recommended Primitive on inputs resident in HBM. The default workload is the
+training-shaped GEMM m=16384 (tokens) k=4096 n=14336, A ~ N(0,1), B ~ N(0,1/k),
+alpha=1, beta=0; with N GPUs the rows of A and D are split into N contiguous
+blocks, B is replicated and there is no communication (total work fixed:
+"strong" scaling). `value` is whole-job TFLOP/s counting 2*m*n*k flops per step
+(the three tensor-core products of the 3xTF32 scheme count once).
+
+Timing: CUDA events on the stream the kernels are launched on (torch's current
+stream, whose handle is passed to the library), after warm-up, bracketed by a
+barrier and a device synchronise, max over ranks. A, B and D together are far
+larger than the 126 MB L2, so every step streams its operands from HBM again.
+
+`e2e` is the same metric through the public Python call
+flash_train.torch.gemm with HOST inputs: every step copies A and B from pinned
+host memory to the device, runs the GEMM and copies D back.
+
+`--impl reference` times the reference's own CPU implementation of the path --
+its PyTorch reference expression alpha*(a@b)+beta*c on CPU tensors -- on the
+host cores, each step a bounded row-slice of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO / "flash-train_b200" / "python"))
+sys.path.insert(0, str(REPO))
+
+WORKLOADS = {
+    # name: (m, k, n, seed, b_scale, alpha, beta, with_c)
+    "gemm_fp32_16384x4096x14336": (16384, 4096, 14336, 3, "rsqrt_k", 1.0, 0.0, False),
+    "gemm_fp32_4096x4096x4096_addend": (4096, 4096, 4096, 1, "one", 1.5, 0.5, True),
+}
+DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
+CPU_SAMPLE_ROWS = 2048  # rows of A per CPU-baseline step
+
+
+def measured_peaks() -> dict:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        return {"source": "measured", **json.loads(path.read_text())}
+    # Earlier measurement on the same pool, used only when the file is absent.
+    return {"source": "fallback", "hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.lines: list[str] = []
+        self.process = None
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            self.process.terminate()  # the exact child started above
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+
+    def summary(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                maxima.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima), "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def make_inputs(workload: str, rank: int, world: int, device):
+    """This rank's A rows, all of B and (if any) this rank's C rows, generated on
+    the CPU from the workload's seed so that every rank and the CPU baseline see
+    the same matrices, then moved to `device`."""
+    import torch
+
+    m, k, n, seed, b_scale, alpha, beta, with_c = WORKLOADS[workload]
+    rows = m // world
+    generator = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=generator)[rank * rows:(rank + 1) * rows].contiguous()
+    b = torch.randn(k, n, generator=generator)
+    if b_scale == "rsqrt_k":
+        b = b / (k ** 0.5)
+    c = torch.randn(m, n, generator=generator)[rank * rows:(rank + 1) * rows].contiguous() if with_c else None
+    if device is not None:
+        a, b = a.to(device), b.to(device)
+        c = c.to(device) if c is not None else None
+    return a, b, c, alpha, beta
+
+
+def cpu_reference_run(workload: str, steps: int, warmup: int) -> dict:
+    """The reference's PyTorch expression on CPU tensors, timed on a row slice."""
+    import torch
+
+    m, k, n, _, _, alpha, beta, with_c = WORKLOADS[workload]
+    a, b, c, alpha, beta = make_inputs(workload, 0, 1, None)
+    rows = min(CPU_SAMPLE_ROWS, m)
+    a, c = a[:rows].contiguous(), (c[:rows].contiguous() if c is not None else None)
+    threads = torch.get_num_threads()
+
+    def step():
+        out = alpha * (a @ b)
+        return out + beta * c if c is not None else out
+
+    for _ in range(max(1, warmup)):
+        step()
+    times = []
+    for _ in range(max(1, steps)):
+        start = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - start)
+    mean = sum(times) / len(times)
+    flops = 2.0 * rows * n * k
+    return {"value": flops / mean / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "reference",
+            "sample": f"first {rows} of {m} rows of A per step (B whole), torch {torch.__version__} CPU float32 "
+                      f"alpha*(a@b)+beta*c, mean of {len(times)} steps after {max(1, warmup)} warm-up",
+            "ms_per_step": mean * 1e3}
+
+
+def run_reference_arm(options) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps = min(options.steps, 5)
+    baseline = cpu_reference_run(options.workload, steps, min(options.warmup, 1))
+    m, k, n, *_ = WORKLOADS[options.workload]
+    line = {
+        "impl": "reference", "metric": "fp32_gemm_tflops", "value": baseline["value"], "unit": "TFLOP/s",
+        "n_gpus": options.gpus, "steps": steps, "warmup": min(options.warmup, 1),
+        "ms_per_step": baseline["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": options.workload, "m": m, "k": k, "n": n,
+                   "note": "reference's PyTorch CPU expression on host cores; each step a bounded row slice"},
+        "cpu_baseline": {key: baseline[key] for key in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": baseline["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def plan_reuse_overhead(capi, torch, device) -> dict:
+    """One Plan for m=n=k=1024, executed 1000 times: host microseconds per enqueue."""
+    from flash_train.capi import GemmBinding, null_operand, tensor_operand
+
+    a = torch.randn(1024, 1024, device=device)
+    b = torch.randn(1024, 1024, device=device)
+    d = torch.empty(1024, 1024, device=device)
+    plan = GemmBinding().make_plan(tensor_operand(a), tensor_operand(b), null_operand(1024, 1024), tensor_operand(d))
+    size = plan.workspace_bytes(0)
+    workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
+    pointer = workspace.data_ptr() if size else 0
+    stream = torch.cuda.current_stream().cuda_stream
+    import ctypes
+
+    execute = capi.lib.ftrainPlanExecutePrimitive
+    handle, ws, st = plan.handle, ctypes.c_void_p(pointer), ctypes.c_void_p(stream)
+    for _ in range(50):
+        execute(handle, 0, ws, size, st)
+    torch.cuda.synchronize()
+    start_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start_event.record()
+    start = time.perf_counter()
+    for _ in range(1000):
+        execute(handle, 0, ws, size, st)
+    host = time.perf_counter() - start
+    end_event.record()
+    torch.cuda.synchronize()
+    return {"primitive": plan.primitive_name(0), "host_us_per_call": host * 1e3,
+            "device_us_per_call": start_event.elapsed_time(end_event),
+            "note": "host time of 1000 ftrainPlanExecutePrimitive calls through ctypes (no sync inside), m=n=k=1024"}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
+    options = parser.parse_args()
+    options.warmup = max(options.warmup, 3) if options.impl == "ours" else options.warmup
+
+    if options.impl == "reference":
+        return run_reference_arm(options)
+
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: this benchmark has no CPU path"}), flush=True)
+        return 1
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    from flash_train import capi  # fails loudly if libflash_train.so is missing
+    import flash_train.torch as ft_torch
+    from flash_train.capi import GemmBinding, null_operand, tensor_operand
+
+    m, k, n, *_ = WORKLOADS[options.workload]
+    if m % world != 0:
+        raise SystemExit(f"m={m} is not divisible by {world} ranks")
+    rows = m // world
+    a, b, c, alpha, beta = make_inputs(options.workload, rank, world, device)
+    d = torch.empty(rows, n, device=device)
+    plan = GemmBinding().make_plan(tensor_operand(a), tensor_operand(b),
+                                   tensor_operand(c) if c is not None else null_operand(rows, n),
+                                   tensor_operand(d), alpha, beta)
+    primitive = plan.primitive_name(0)
+    size = plan.workspace_bytes(0)
+    workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
+    pointer = workspace.data_ptr() if size else 0
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        plan.execute(0, pointer, size, stream)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(options.warmup):
+        step()
+    barrier()
+    start_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = capi.launch_count()
+    with ClockSampler(local_rank) as sampler:
+        start_event.record()
+        for _ in range(options.steps):
+            step()
+        end_event.record()
+        barrier()
+        elapsed_ms = start_event.elapsed_time(end_event)
+    launches = capi.launch_count() - launches_before
+    clocks = sampler.summary()
+    if distributed:
+        slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(slowest.item())
+    ms_per_step = elapsed_ms / options.steps
+    total_flops = 2.0 * m * n * k
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public Python call, host buffers in, host buffer out ----
+    e2e = None
+    if not options.no_extras:
+        a_host, b_host = a.cpu().pin_memory(), b.cpu().pin_memory()
+        c_host = c.cpu().pin_memory() if c is not None else None
+        d_host = torch.empty(rows, n).pin_memory()
+        e2e_steps = max(3, min(options.steps, 10))
+
+        def e2e_step():
+            a_dev = a_host.to(device, non_blocking=True)
+            b_dev = b_host.to(device, non_blocking=True)
+            c_dev = c_host.to(device, non_blocking=True) if c_host is not None else None
+            out = ft_torch.gemm(a_dev, b_dev, c_dev, alpha=alpha, beta=beta)
+            d_host.copy_(out, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e2e_end.record()
+        barrier()
+        e2e_ms = e2e_start.elapsed_time(e2e_end)
+        if distributed:
+            slowest = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+            e2e_ms = float(slowest.item())
+        h2d = (a_host.numel() + b_host.numel() + (c_host.numel() if c_host is not None else 0)) * 4
+        e2e = {"value": total_flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d_host.numel() * 4, "steps": e2e_steps,
+               "ms_per_step": e2e_ms / e2e_steps, "api": "flash_train.torch.gemm"}
+
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return 0
+
+    peaks = measured_peaks()
+    # 3xTF32 roofline in FP32-equivalent flops: TF32 dense = BF16 dense / 2, and
+    # three tensor-core products per FP32 product. The kernel is timed inside a
+    # long step, so the sustained BF16 figure applies.
+    tensor_peak = peaks["bf16_tflops_sustained"] / 6.0
+    per_gpu = value / world
+    if primitive.startswith("Fp32Gemm3xTf32"):
+        roofline = {"bound": "tensor", "achieved": per_gpu, "peak": tensor_peak, "unit": "TFLOP/s",
+                    "frac": per_gpu / tensor_peak, "traffic": None,
+                    "peak_source": f"{peaks['source']} bf16_tflops_sustained / 6 (TF32 = BF16/2; 3 MMAs per product)",
+                    "kernel": "tensorGemm3xTf32", "ms_per_launch": ms_per_step}
+    else:
+        fp32_peak = 148 * 128 * 2 * 1.965e9 / 1e12
+        roofline = {"bound": "tensor", "achieved": per_gpu, "peak": fp32_peak, "unit": "TFLOP/s",
+                    "frac": per_gpu / fp32_peak, "traffic": None,
+                    "peak_source": "nominal FFMA rate 148 SMs x 128 lanes x 2 x 1.965 GHz", "kernel": primitive,
+                    "ms_per_launch": ms_per_step}
+
+    line = {
+        "metric": "fp32_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": options.steps,
+        "warmup": options.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": options.workload, "m": m, "k": k, "n": n, "rows_per_gpu": rows,
+                   "partition": "rows of A and D split across GPUs, B replicated, no communication",
+                   "primitive": primitive, "workspace_bytes": size,
+                   "l2": "operands (A+B+D > 1 GB per GPU at N=1) exceed the 126 MB L2, so each step re-reads HBM"},
+        "roofline": roofline, "clocks": clocks, "gpu_launches": launches,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if not options.no_extras:
+        line["plan_reuse"] = plan_reuse_overhead(capi, torch, device)
+        if world == 1:
+            baseline = cpu_reference_run(options.workload, 3, 1)
+            line["cpu_baseline"] = {key: baseline[key] for key in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,83 @@
+// The GEMM entry points of ftcuda/ftcuda.h: dispatch on the kernel family.
+#include <cuda_runtime_api.h>
+
+#include <cstring>
+#include <type_traits>
+
+#include "gemm_kernels.hpp"
+
+namespace {
+
+using ftcuda::LaunchState;
+
+static_assert(std::is_trivially_copyable<LaunchState>::value, "a launch must be copyable with the Primitive");
+
+const char* supports(int kernel, const FtcudaGemmDesc& desc) {
+    switch (kernel) {
+        case FTCUDA_GEMM_SIMT: return ftcuda::supportsSimt(desc, false);
+        case FTCUDA_GEMM_SIMT_SPLITK: return ftcuda::supportsSimt(desc, true);
+        case FTCUDA_GEMM_TF32X3: return ftcuda::supportsTensor(desc, false);
+        case FTCUDA_GEMM_TF32X3_SPLITK: return ftcuda::supportsTensor(desc, true);
+        case FTCUDA_GEMM_SKINNY: return ftcuda::supportsSkinny(desc);
+        default: return "unknown kernel family";
+    }
+}
+
+}  // namespace
+
+extern "C" int ftcuda_gemm_supports(int kernel, const FtcudaGemmDesc* desc, char* message, size_t message_capacity) {
+    if (desc == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null descriptor"); }
+    const char* reason = supports(kernel, *desc);
+    if (reason != nullptr) { return ftcuda::fail(message, message_capacity, 1, "%s", reason); }
+    return 0;
+}
+
+extern "C" int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, FtcudaGemmLaunch* launch, char* message,
+                                     size_t message_capacity) {
+    if (desc == nullptr || launch == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null argument"); }
+    const char* reason = supports(kernel, *desc);
+    if (reason != nullptr) { return ftcuda::fail(message, message_capacity, 1, "%s", reason); }
+    std::memset(launch, 0, sizeof *launch);
+    LaunchState& state = *reinterpret_cast<LaunchState*>(launch);
+    state.desc         = *desc;
+    state.kernel       = kernel;
+    switch (kernel) {
+        case FTCUDA_GEMM_SIMT: return ftcuda::configureSimt(state, false, message, message_capacity);
+        case FTCUDA_GEMM_SIMT_SPLITK: return ftcuda::configureSimt(state, true, message, message_capacity);
+        case FTCUDA_GEMM_TF32X3: return ftcuda::configureTensor(state, false, message, message_capacity);
+        case FTCUDA_GEMM_TF32X3_SPLITK: return ftcuda::configureTensor(state, true, message, message_capacity);
+        default: return ftcuda::configureSkinny(state, message, message_capacity);
+    }
+}
+
+extern "C" uint64_t ftcuda_gemm_workspace_bytes(const FtcudaGemmLaunch* launch) {
+    return launch == nullptr ? 0 : reinterpret_cast<const LaunchState*>(launch)->workspace_bytes;
+}
+
+extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                  void* stream, char* message, size_t message_capacity) {
+    if (launch == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null launch"); }
+    const LaunchState& state = *reinterpret_cast<const LaunchState*>(launch);
+    if (workspace_bytes < state.workspace_bytes || (state.workspace_bytes != 0 && workspace == nullptr)) {
+        return ftcuda::fail(message, message_capacity, 1, "workspace of %llu bytes needed",
+                            static_cast<unsigned long long>(state.workspace_bytes));
+    }
+    // A kernel of an earlier launch on this device gave up on a wait: the
+    // device-side pipeline is not trustworthy any more.
+    if (state.host_status != nullptr && *state.host_status != 0) {
+        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)",
+                            *state.host_status);
+    }
+    const cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+    cudaError_t error              = cudaSuccess;
+    switch (state.kernel) {
+        case FTCUDA_GEMM_SIMT:
+        case FTCUDA_GEMM_SIMT_SPLITK: error = ftcuda::launchSimt(state, workspace, cuda_stream); break;
+        case FTCUDA_GEMM_TF32X3:
+        case FTCUDA_GEMM_TF32X3_SPLITK: error = ftcuda::launchTensor(state, workspace, cuda_stream); break;
+        case FTCUDA_GEMM_SKINNY: error = ftcuda::launchSkinny(state, cuda_stream); break;
+        default: return ftcuda::fail(message, message_capacity, 1, "unknown kernel family %d", state.kernel);
+    }
+    if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+    return 0;
+}

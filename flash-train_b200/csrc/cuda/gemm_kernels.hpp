@@ -1,0 +1,94 @@
+// Internal interface of the CUDA platform subtree: the in-memory form of a
+// configured launch and the per-kernel-family host entry points that the
+// C ABI in ftcuda_gemm.cu dispatches to.
+#ifndef FTCUDA_GEMM_KERNELS_HPP_
+#define FTCUDA_GEMM_KERNELS_HPP_
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "ftcuda/ftcuda.h"
+
+namespace ftcuda {
+
+// How an operand tile reaches the kernel.
+enum Variant : int {
+    kVariantGeneric  = 0,  // predicated loads, any strides (SIMT only)
+    kVariantTmaAk    = 1,  // TMA; A rows contiguous along K (row-major A)
+    kVariantTmaAm    = 2,  // TMA; A contiguous along M (transposed view of a K x M buffer)
+};
+
+// What ftcuda_gemm_configure stores inside an FtcudaGemmLaunch.
+struct LaunchState {
+    alignas(64) CUtensorMap map_a;
+    alignas(64) CUtensorMap map_b;
+    FtcudaGemmDesc desc;
+    std::int32_t kernel;
+    std::int32_t variant;
+    std::uint32_t grid_x, grid_y, grid_z;
+    std::uint32_t block;
+    std::uint32_t smem_bytes;
+    std::uint32_t splits;          // K slices (1 = no split)
+    std::uint32_t k_per_split;     // K elements per slice, a multiple of the K tile
+    std::uint32_t chunk_k_blocks;  // tensor kernel: K blocks accumulated in TMEM between drains
+    std::uint32_t row_tile;        // skinny kernel: rows of A kept per thread
+    std::uint64_t workspace_bytes;
+    int* device_status;            // mapped host word the kernels report a timed-out wait in
+    const volatile int* host_status;
+};
+static_assert(sizeof(LaunchState) <= sizeof(FtcudaGemmLaunch), "launch blob too small");
+static_assert(alignof(FtcudaGemmLaunch) >= 64, "launch blob must be 64-byte aligned");
+
+inline std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y; }
+
+// Writes a message (if a buffer is given) and returns `code`.
+int fail(char* message, std::size_t capacity, int code, const char* format, ...);
+
+// ---- runtime helpers (ftcuda_runtime.cu) ----
+
+// SM count of `device`, cached. Returns false (with message) on a CUDA error.
+bool deviceSmCount(int device, int* sm_count, char* message, std::size_t capacity);
+// Per-device status word in mapped pinned host memory; nonzero after a kernel
+// gave up on a wait. Returns false (with message) on a CUDA error.
+bool deviceStatusWord(int device, int** device_pointer, const volatile int** host_pointer, char* message,
+                      std::size_t capacity);
+// Encodes a 2-D FP32 tiled TMA descriptor: `inner` contiguous elements per row,
+// `outer` rows, `row_pitch_bytes` between rows, box = box_inner x box_outer.
+bool encodeTensorMap2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t outer,
+                       std::uint64_t row_pitch_bytes, std::uint32_t box_inner, std::uint32_t box_outer,
+                       bool swizzle_128b, char* message, std::size_t capacity);
+void countLaunches(std::uint64_t launches);
+
+// True when `base`/strides describe a matrix TMA can fetch with `contiguous`
+// as the unit-stride dimension: unit stride there, 16-byte aligned base,
+// row pitch a positive multiple of 16 bytes that fits 2^40, extents < 2^32.
+bool tmaEligible(const void* base, std::int64_t contiguous_stride, std::int64_t other_stride,
+                 std::uint64_t contiguous_extent, std::uint64_t other_extent);
+
+// ---- kernel families ----
+// supports*: nullptr when the family can run the problem, else the reason.
+// configure*: fills `state` (desc, kernel already set); 0 on success.
+// launch*: enqueues; returns the CUDA error of the launch.
+
+const char* supportsSimt(const FtcudaGemmDesc& desc, bool split_k);
+int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t capacity);
+cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream);
+
+const char* supportsSkinny(const FtcudaGemmDesc& desc);
+int configureSkinny(LaunchState& state, char* message, std::size_t capacity);
+cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream);
+
+const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k);
+int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t capacity);
+cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream);
+
+// D = alpha * sum_s partial[s] + beta * C over `splits` dense m x n partials.
+cudaError_t launchSplitKReduce(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,
+                               cudaStream_t stream);
+
+}  // namespace ftcuda
+
+#endif

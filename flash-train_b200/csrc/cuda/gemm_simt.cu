@@ -1,0 +1,459 @@
+// Exact-FP32 GEMM on the SIMT pipes: D = alpha * A * B + beta * C with every
+// product and sum in IEEE FP32 (FFMA), sequential over K inside one thread --
+// the arithmetic of the reference kernel (src/primitive/hygon/gemm/fp32_gemm.hip:18-31),
+// re-tiled for B200.
+//
+// Two kernels:
+//   * simtGemmTma: 128x128 output tile per CTA, 256 threads, 8x8 outputs per
+//     thread. K is walked in blocks of 32. Operand tiles are fetched by TMA
+//     into a 3-stage shared-memory ring guarded by mbarriers, so the copy of
+//     blocks i+1 and i+2 overlaps the FFMA work on block i. The A tile is
+//     stored with the 128-byte swizzle so that the 8 rows a thread owns are
+//     read as bank-conflict-free 128-bit loads. Two CTAs are resident per SM
+//     (96 KiB of shared memory each). The epilogue swaps half-rows between
+//     the two half-warps with shuffles so that each store instruction of a
+//     warp writes one full 512-byte row segment.
+//   * simtGemmGeneric: 64x64 tile with predicated scalar loads; takes any
+//     strides, any alignment, tiny shapes and K == 0. It is the path for
+//     layouts TMA cannot describe.
+// Both can restrict themselves to one K slice (blockIdx.z) and write the raw
+// partial tile to a workspace, which the split-K reduction finishes.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "gemm_kernels.hpp"
+#include "ptx.cuh"
+
+namespace ftcuda {
+namespace {
+
+constexpr int kTileM   = 128;
+constexpr int kTileN   = 128;
+constexpr int kTileK   = 32;
+constexpr int kStages  = 3;
+constexpr int kThreads = 256;
+constexpr int kTileBytes  = kTileM * kTileK * 4;  // 16 KiB for either operand
+constexpr int kStageBytes = 2 * kTileBytes;
+// 1024 bytes of slack lets the kernel align the ring to the swizzle atom.
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 64;
+
+struct SimtParams {
+    const float* c;
+    float* d;
+    std::int64_t c_row_stride, c_col_stride;
+    std::int64_t d_row_stride, d_col_stride;
+    std::uint32_t m, n, k;
+    std::uint32_t k_per_split;  // K elements per blockIdx.z slice
+    float alpha, beta;
+    float* partials;            // non-null: write raw sums to partials[z][m][n]
+    int* status;
+};
+
+// Output stage shared by both kernels' slow path: one element, any strides.
+__device__ __forceinline__ void storeElement(const SimtParams& p, std::uint32_t row, std::uint32_t col, float sum) {
+    if (row >= p.m || col >= p.n) { return; }
+    if (p.partials != nullptr) {
+        p.partials[(static_cast<std::uint64_t>(blockIdx.z) * p.m + row) * p.n + col] = sum;
+        return;
+    }
+    float value = p.alpha * sum;
+    if (p.c != nullptr) {
+        value += p.beta * p.c[static_cast<std::int64_t>(row) * p.c_row_stride + static_cast<std::int64_t>(col) * p.c_col_stride];
+    }
+    p.d[static_cast<std::int64_t>(row) * p.d_row_stride + static_cast<std::int64_t>(col) * p.d_col_stride] = value;
+}
+
+// kAContiguousK: the A tile is [128 rows][32 k] with 128-byte rows, swizzled;
+// otherwise it is [32 k][128 rows], linear (A was given contiguous along M).
+template<bool kAContiguousK>
+__global__ void __launch_bounds__(kThreads, 2)
+simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const SimtParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // Ring of stages at a 1024-byte boundary, barriers behind it.
+    const std::uint32_t ring_offset = (1024 - (smemAddress(smem_raw) & 1023)) & 1023;
+    unsigned char* ring             = smem_raw + ring_offset;
+    std::uint64_t* full             = reinterpret_cast<std::uint64_t*>(ring + kStages * kStageBytes);
+    __shared__ int abort_flag;
+
+    const int tid  = threadIdx.x;
+    const int tx   = tid & 15;
+    const int ty   = tid >> 4;
+    const int lane = tid & 31;
+
+    const std::uint32_t tile_m = blockIdx.y * kTileM;
+    const std::uint32_t tile_n = blockIdx.x * kTileN;
+    const std::uint32_t k_begin = blockIdx.z * p.k_per_split;
+    const std::uint32_t k_end   = min(p.k, k_begin + p.k_per_split);
+    const int k_blocks          = static_cast<int>((k_end - k_begin + kTileK - 1) / kTileK);
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) { mbarrierInit(&full[s], 1); }
+        fenceBarrierInit();
+        prefetchTensorMap(&map_a);
+        prefetchTensorMap(&map_b);
+    }
+    __syncthreads();
+
+    // One thread feeds the ring. Out-of-range parts of a box (M, N and K
+    // tails) arrive as zeros, which contribute nothing to the sums.
+    auto issue = [&](int block) {
+        const int s                = block % kStages;
+        unsigned char* stage       = ring + s * kStageBytes;
+        const std::int32_t k_coord = static_cast<std::int32_t>(k_begin + block * kTileK);
+        mbarrierArriveExpectTx(&full[s], kStageBytes);
+        if (kAContiguousK) {
+            tmaLoad2d(stage, &map_a, &full[s], k_coord, static_cast<std::int32_t>(tile_m));
+        } else {
+            tmaLoad2d(stage, &map_a, &full[s], static_cast<std::int32_t>(tile_m), k_coord);
+        }
+        tmaLoad2d(stage + kTileBytes, &map_b, &full[s], static_cast<std::int32_t>(tile_n), k_coord);
+    };
+    if (tid == 0) {
+        for (int block = 0; block < kStages - 1 && block < k_blocks; ++block) { issue(block); }
+    }
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc[i][j] = 0.0F; }
+    }
+
+    bool healthy = true;
+    for (int block = 0; block < k_blocks; ++block) {
+        const int s = block % kStages;
+        // Refill the stage that block-1 used (all threads passed the barrier at
+        // the end of that iteration, so nobody reads it any more).
+        if (tid == 0 && block + kStages - 1 < k_blocks) { issue(block + kStages - 1); }
+        if (!mbarrierWait(&full[s], (block / kStages) & 1, &abort_flag)) {
+            abort_flag = 1;
+            healthy    = false;
+        }
+        // A timed-out wait is reported and the tile abandoned, by every thread
+        // together: __syncthreads_or makes the decision uniform.
+        if (__syncthreads_or(healthy ? 0 : 1)) {
+            healthy = false;
+            break;
+        }
+        const unsigned char* a_tile = ring + s * kStageBytes;
+        const unsigned char* b_tile = a_tile + kTileBytes;
+#pragma unroll
+        for (int k4 = 0; k4 < kTileK / 4; ++k4) {
+            float a_frag[8][4];
+            if (kAContiguousK) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int row      = ty * 8 + i;
+                    const float4 value = *reinterpret_cast<const float4*>(a_tile + row * 128 + ((k4 ^ (row & 7)) << 4));
+                    a_frag[i][0] = value.x;
+                    a_frag[i][1] = value.y;
+                    a_frag[i][2] = value.z;
+                    a_frag[i][3] = value.w;
+                }
+            } else {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const float4* row = reinterpret_cast<const float4*>(a_tile + (k4 * 4 + kk) * (kTileM * 4) + ty * 32);
+                    const float4 lo   = row[0];
+                    const float4 hi   = row[1];
+                    a_frag[0][kk] = lo.x;
+                    a_frag[1][kk] = lo.y;
+                    a_frag[2][kk] = lo.z;
+                    a_frag[3][kk] = lo.w;
+                    a_frag[4][kk] = hi.x;
+                    a_frag[5][kk] = hi.y;
+                    a_frag[6][kk] = hi.z;
+                    a_frag[7][kk] = hi.w;
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const unsigned char* b_row = b_tile + (k4 * 4 + kk) * (kTileN * 4);
+                const float4 b0            = *reinterpret_cast<const float4*>(b_row + tx * 16);
+                const float4 b1            = *reinterpret_cast<const float4*>(b_row + 256 + tx * 16);
+                const float b_frag[8]      = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { acc[i][j] = fmaf(a_frag[i][kk], b_frag[j], acc[i][j]); }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (!healthy) {
+        // Give up on the tile: report, then let the copies that are still in
+        // flight land (bounded) before the CTA's shared memory is released.
+        if (tid == 0) {
+            if (p.status != nullptr) { *p.status = 1; }
+            int never = 0;
+            for (int s = 0; s < kStages; ++s) {
+                mbarrierWait(&full[s], 0, &never);
+                mbarrierWait(&full[s], 1, &never);
+            }
+        }
+        return;
+    }
+
+    // Epilogue. Lanes 0-15 of a warp own rows ty_even*8+i, lanes 16-31 rows
+    // ty_odd*8+i, each as two 4-column groups (tx*4.. and 64+tx*4..). One
+    // shuffle round trades half-rows so that, per store instruction, the 32
+    // lanes cover 128 consecutive columns of ONE row.
+    const bool upper          = lane >= 16;
+    const std::uint32_t col   = tile_n + (upper ? 64 : 0) + tx * 4;
+    const std::uint32_t row_a = tile_m + (ty & ~1) * 8;  // row block of the even half-warp
+    float* out                = p.partials != nullptr
+                                    ? p.partials + static_cast<std::uint64_t>(blockIdx.z) * p.m * p.n
+                                    : p.d;
+    const std::int64_t out_row_stride = p.partials != nullptr ? p.n : p.d_row_stride;
+    const std::int64_t out_col_stride = p.partials != nullptr ? 1 : p.d_col_stride;
+    const bool scale                  = p.partials == nullptr;
+    const bool with_c                 = scale && p.c != nullptr;
+    const bool vector_ok =
+        out_col_stride == 1 && (out_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(out) & 15) == 0 &&
+        (p.n & 3) == 0 &&
+        (!with_c || (p.c_col_stride == 1 && (p.c_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(p.c) & 15) == 0));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 first  = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        const float4 second = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        const float4 send   = upper ? first : second;
+        float4 recv;
+        recv.x = __shfl_xor_sync(0xFFFFFFFFU, send.x, 16);
+        recv.y = __shfl_xor_sync(0xFFFFFFFFU, send.y, 16);
+        recv.z = __shfl_xor_sync(0xFFFFFFFFU, send.z, 16);
+        recv.w = __shfl_xor_sync(0xFFFFFFFFU, send.w, 16);
+        const float4 part[2]       = {upper ? recv : first, upper ? second : recv};
+        const std::uint32_t row[2] = {row_a + i, row_a + 8 + i};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (row[h] >= p.m) { continue; }
+            if (vector_ok) {
+                if (col >= p.n) { continue; }
+                float4 value = part[h];
+                if (scale) {
+                    value.x *= p.alpha;
+                    value.y *= p.alpha;
+                    value.z *= p.alpha;
+                    value.w *= p.alpha;
+                }
+                if (with_c) {
+                    const float4 addend =
+                        *reinterpret_cast<const float4*>(p.c + static_cast<std::int64_t>(row[h]) * p.c_row_stride + col);
+                    value.x += p.beta * addend.x;
+                    value.y += p.beta * addend.y;
+                    value.z += p.beta * addend.z;
+                    value.w += p.beta * addend.w;
+                }
+                *reinterpret_cast<float4*>(out + static_cast<std::int64_t>(row[h]) * out_row_stride + col) = value;
+            } else {
+                storeElement(p, row[h], col + 0, part[h].x);
+                storeElement(p, row[h], col + 1, part[h].y);
+                storeElement(p, row[h], col + 2, part[h].z);
+                storeElement(p, row[h], col + 3, part[h].w);
+            }
+        }
+    }
+}
+
+// ---- generic path ----
+
+constexpr int kGenericTile = 64;
+constexpr int kGenericK    = 16;
+
+struct GenericParams {
+    const float* a;
+    const float* b;
+    std::int64_t a_row_stride, a_col_stride;
+    std::int64_t b_row_stride, b_col_stride;
+    SimtParams out;
+};
+
+__global__ void __launch_bounds__(256) simtGemmGeneric(const GenericParams g) {
+    __shared__ float a_tile[kGenericK][kGenericTile + 4];
+    __shared__ float b_tile[kGenericK][kGenericTile + 4];
+    const SimtParams& p = g.out;
+    const int tid       = threadIdx.x;
+    const int tx        = tid & 15;
+    const int ty        = tid >> 4;
+    const std::uint32_t tile_m  = blockIdx.y * kGenericTile;
+    const std::uint32_t tile_n  = blockIdx.x * kGenericTile;
+    const std::uint32_t k_begin = blockIdx.z * p.k_per_split;
+    const std::uint32_t k_end   = min(p.k, k_begin + p.k_per_split);
+
+    float acc[4][4] = {};
+    for (std::uint32_t k0 = k_begin; k0 < k_end; k0 += kGenericK) {
+        // 64 x 16 elements per operand, 4 per thread; consecutive threads walk
+        // the K index of A and the N index of B.
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int index         = tid + e * 256;
+            const int a_k           = index & 15;
+            const int a_m           = index >> 4;
+            const std::uint32_t row = tile_m + a_m;
+            const std::uint32_t kk  = k0 + a_k;
+            a_tile[a_k][a_m] = (row < p.m && kk < k_end)
+                                   ? g.a[static_cast<std::int64_t>(row) * g.a_row_stride + static_cast<std::int64_t>(kk) * g.a_col_stride]
+                                   : 0.0F;
+            const int b_n            = index & 63;
+            const int b_k            = index >> 6;
+            const std::uint32_t col  = tile_n + b_n;
+            const std::uint32_t kk_b = k0 + b_k;
+            b_tile[b_k][b_n] = (col < p.n && kk_b < k_end)
+                                   ? g.b[static_cast<std::int64_t>(kk_b) * g.b_row_stride + static_cast<std::int64_t>(col) * g.b_col_stride]
+                                   : 0.0F;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kGenericK; ++kk) {
+            float a_frag[4];
+            float b_frag[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a_frag[i] = a_tile[kk][ty * 4 + i];
+                b_frag[i] = b_tile[kk][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { acc[i][j] = fmaf(a_frag[i], b_frag[j], acc[i][j]); }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { storeElement(p, tile_m + ty * 4 + i, tile_n + tx * 4 + j, acc[i][j]); }
+    }
+}
+
+SimtParams makeOutputParams(const LaunchState& state, void* workspace) {
+    const FtcudaGemmDesc& desc = state.desc;
+    SimtParams p{};
+    p.c            = desc.c;
+    p.d            = desc.d;
+    p.c_row_stride = desc.c_row_stride;
+    p.c_col_stride = desc.c_col_stride;
+    p.d_row_stride = desc.d_row_stride;
+    p.d_col_stride = desc.d_col_stride;
+    p.m            = static_cast<std::uint32_t>(desc.m);
+    p.n            = static_cast<std::uint32_t>(desc.n);
+    p.k            = static_cast<std::uint32_t>(desc.k);
+    p.k_per_split  = state.k_per_split;
+    p.alpha        = desc.alpha;
+    p.beta         = desc.beta;
+    p.partials     = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
+    p.status       = state.device_status;
+    return p;
+}
+
+}  // namespace
+
+const char* supportsSimt(const FtcudaGemmDesc& desc, bool split_k) {
+    if (desc.m >= (1ULL << 31) || desc.n >= (1ULL << 31) || desc.k >= (1ULL << 31)) {
+        return "an extent does not fit 31 bits";
+    }
+    if (ceilDiv(desc.m, kGenericTile) > 65535) { return "more than 65535 row tiles"; }
+    if (split_k) {
+        if (desc.m * desc.n == 0) { return "the output is empty"; }
+        if (desc.k < 2 * 256) { return "K is too short to split"; }
+    }
+    return nullptr;
+}
+
+int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t capacity) {
+    const FtcudaGemmDesc& desc = state.desc;
+    int sms                    = 0;
+    if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
+    if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
+
+    // TMA path: both operands describable and at least one full-size tile of
+    // work; otherwise the generic kernel.
+    const bool b_ok  = tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    const bool a_k   = tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m);
+    const bool a_m   = tmaEligible(desc.a, desc.a_row_stride, desc.a_col_stride, desc.m, desc.k);
+    const bool large = desc.m >= 96 && desc.n >= 96 && desc.k >= 32;
+    state.variant    = kVariantGeneric;
+    if (b_ok && large && (a_k || a_m)) { state.variant = a_k ? kVariantTmaAk : kVariantTmaAm; }
+
+    const std::uint32_t tile_m = state.variant == kVariantGeneric ? kGenericTile : kTileM;
+    const std::uint32_t tile_n = state.variant == kVariantGeneric ? kGenericTile : kTileN;
+    const std::uint32_t tile_k = state.variant == kVariantGeneric ? kGenericK : kTileK;
+    state.grid_x               = static_cast<std::uint32_t>(ceilDiv(desc.n, tile_n));
+    state.grid_y               = static_cast<std::uint32_t>(ceilDiv(desc.m, tile_m));
+    state.block                = kThreads;
+    state.smem_bytes           = state.variant == kVariantGeneric ? 0 : kSmemBytes;
+
+    state.splits      = 1;
+    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(desc.k == 0 ? 1 : desc.k, tile_k) * tile_k);
+    if (split_k) {
+        // Enough K slices to give every SM two CTAs, each slice at least 256 deep.
+        const std::uint64_t tiles = static_cast<std::uint64_t>(state.grid_x) * state.grid_y;
+        std::uint64_t splits      = ceilDiv(2ULL * sms, tiles);
+        const std::uint64_t most  = desc.k / 256;
+        if (splits > most) { splits = most; }
+        if (splits > 64) { splits = 64; }
+        if (splits < 2) { splits = 2; }
+        state.k_per_split = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, splits), tile_k) * tile_k);
+        state.splits      = static_cast<std::uint32_t>(ceilDiv(desc.k, state.k_per_split));
+    }
+    state.grid_z          = state.splits;
+    state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
+
+    if (state.variant != kVariantGeneric) {
+        const std::uint64_t a_pitch =
+            static_cast<std::uint64_t>(state.variant == kVariantTmaAk ? desc.a_row_stride : desc.a_col_stride) * sizeof(float);
+        const bool a_encoded =
+            state.variant == kVariantTmaAk
+                ? encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m, a_pitch, kTileK, kTileM, true, message, capacity)
+                : encodeTensorMap2d(&state.map_a, desc.a, desc.m, desc.k, a_pitch, kTileM, kTileK, false, message, capacity);
+        if (!a_encoded) { return 1; }
+        if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
+                               static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), kTileN, kTileK, false,
+                               message, capacity)) {
+            return 1;
+        }
+        // Opting in to 97 KiB of dynamic shared memory is a per-device setting.
+        cudaError_t error = cudaFuncSetAttribute(simtGemmTma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (error == cudaSuccess) {
+            error = cudaFuncSetAttribute(simtGemmTma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        }
+        if (error != cudaSuccess) {
+            return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error));
+        }
+    }
+    return 0;
+}
+
+cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream) {
+    const SimtParams out = makeOutputParams(state, workspace);
+    const dim3 grid(state.grid_x, state.grid_y, state.grid_z);
+    if (state.variant == kVariantGeneric) {
+        GenericParams g{};
+        g.a            = state.desc.a;
+        g.b            = state.desc.b;
+        g.a_row_stride = state.desc.a_row_stride;
+        g.a_col_stride = state.desc.a_col_stride;
+        g.b_row_stride = state.desc.b_row_stride;
+        g.b_col_stride = state.desc.b_col_stride;
+        g.out          = out;
+        simtGemmGeneric<<<grid, state.block, 0, stream>>>(g);
+    } else if (state.variant == kVariantTmaAk) {
+        simtGemmTma<true><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+    } else {
+        simtGemmTma<false><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+    }
+    cudaError_t error = cudaGetLastError();
+    std::uint64_t launches = 1;
+    if (error == cudaSuccess && state.splits > 1) {
+        error = launchSplitKReduce(state.desc, static_cast<const float*>(workspace), state.splits, stream);
+        ++launches;
+    }
+    countLaunches(launches);
+    return error;
+}
+
+}  // namespace ftcuda

@@ -1,0 +1,577 @@
+// FP32 GEMM on the 5th-generation tensor cores by 3xTF32 split precision:
+//   a = a_hi + a_lo, b = b_hi + b_lo with every part a TF32 number, and
+//   a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi,
+// three tcgen05.mma.kind::tf32 products accumulated in FP32 in tensor memory.
+// The dropped a_lo*b_lo term is below 2^-22 of |a*b|.
+//
+// One CTA per SM, persistent over 128 x 256 output tiles, K walked in blocks
+// of 32. Sixteen warps in four roles, connected only by mbarriers:
+//
+//   warp 0      TMA producer. Per K block it fetches the 128x32 A tile straight
+//               into the stage's A_hi buffer (128-byte swizzle: already the
+//               K-major layout the MMA wants) and the 32x256 B tile as eight
+//               32(k) x 32(n) swizzled boxes into a small raw ring.
+//   warps 4-7   converters. They split A in place (A_hi overwritten with the
+//               TF32-rounded value, A_lo next to it) and transpose-and-split
+//               the raw B boxes into K-major B_hi / B_lo tiles, so both MMA
+//               operands are K-major with the 128-byte swizzle. Reads and
+//               writes are arranged to be bank-conflict free (lane <-> k).
+//   warp 1      MMA issuer (one thread): 4 K-steps x 3 products per K block
+//               into the "chunk" accumulator (TMEM columns 0-255); a
+//               tcgen05.commit per K block hands the stage back to the producer.
+//   warps 8-15  drain / epilogue. Every `chunk_k_blocks` K blocks the chunk
+//               accumulator is added, in round-to-nearest FP32, to a running
+//               sum kept in TMEM columns 256-511, and the chunk restarts from
+//               zero. This bounds the length of any accumulation chain inside
+//               the tensor core, whose internal FP32 additions are not
+//               round-to-nearest. After the last chunk the sum is scaled and
+//               written out (or stored raw as a split-K partial) while the
+//               next tile's first chunk is already being multiplied.
+//
+// Shared memory: 2 stages x (A_hi 16 + A_lo 16 + B_hi 32 + B_lo 32 KiB) plus a
+// 2 x 16 KiB raw-B ring = 224 KiB. Tensor memory: all 512 columns.
+//
+// Every wait is bounded (ptx.cuh). A wait that gives up raises the CTA's abort
+// flag; all roles then stop, outstanding copies and MMAs are given time to
+// land, tensor memory is freed and the device status word is set to nonzero,
+// which the host reports at the next launch.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "gemm_kernels.hpp"
+#include "ptx.cuh"
+
+namespace ftcuda {
+namespace {
+
+constexpr int kTileM  = 128;
+constexpr int kTileN  = 256;
+constexpr int kTileK  = 32;
+constexpr int kStages = 2;
+
+constexpr int kAHiOffset    = 0;
+constexpr int kALoOffset    = 16384;
+constexpr int kBHiOffset    = 32768;
+constexpr int kBLoOffset    = 65536;
+constexpr int kStageBytes   = 98304;
+constexpr int kRawSlotBytes = 16384;  // 32 k x 128 n, as four 4 KiB boxes
+constexpr int kRawOffset    = kStages * kStageBytes;
+constexpr int kBarrierOffset = kRawOffset + 2 * kRawSlotBytes;
+constexpr int kSmemBytes     = kBarrierOffset + 256 + 1024;  // + barriers + alignment slack
+
+constexpr int kThreads        = 512;
+constexpr int kProducerWarp   = 0;
+constexpr int kMmaWarp        = 1;
+constexpr int kFirstConverter = 4;   // warps 4..7
+constexpr int kFirstEpilogue  = 8;   // warps 8..15
+constexpr int kTmemColumns    = 512;
+constexpr int kRunningColumn  = 256;
+
+// Rows of M tiles walked together so that concurrently running CTAs share B
+// panels in L2.
+constexpr std::uint32_t kGroupM = 16;
+
+struct TensorParams {
+    const float* c;
+    float* d;
+    std::int64_t c_row_stride, c_col_stride;
+    std::int64_t d_row_stride, d_col_stride;
+    std::uint32_t m, n, k;
+    std::uint32_t tiles_m, tiles_n;
+    std::uint32_t splits, k_per_split;
+    std::uint32_t chunk_k_blocks;
+    float alpha, beta;
+    float* partials;  // non-null: raw sums to partials[split][m][n]
+    int* status;
+};
+
+struct Barriers {
+    std::uint64_t a_full[kStages];
+    std::uint64_t mma_done[kStages];
+    std::uint64_t conv_done[kStages];
+    std::uint64_t raw_full[2];
+    std::uint64_t raw_empty[2];
+    std::uint64_t acc_full;
+    std::uint64_t acc_empty;
+    std::uint64_t flush;
+    std::uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct WorkItem {
+    std::uint32_t tile_m, tile_n;  // element offsets
+    std::uint32_t split;
+    std::uint32_t k_begin, k_blocks;
+};
+
+__device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint32_t item) {
+    const std::uint32_t tiles = p.tiles_m * p.tiles_n;
+    WorkItem w;
+    w.split                   = item / tiles;
+    const std::uint32_t tile  = item - w.split * tiles;
+    const std::uint32_t band  = tile / (kGroupM * p.tiles_n);
+    const std::uint32_t first = band * kGroupM;
+    const std::uint32_t rows  = min(kGroupM, p.tiles_m - first);
+    const std::uint32_t rest  = tile - band * kGroupM * p.tiles_n;
+    w.tile_m                  = (first + rest % rows) * kTileM;
+    w.tile_n                  = (rest / rows) * kTileN;
+    w.k_begin                 = w.split * p.k_per_split;
+    const std::uint32_t k_end = min(p.k, w.k_begin + p.k_per_split);
+    w.k_blocks                = (k_end - w.k_begin + kTileK - 1) / kTileK;
+    return w;
+}
+
+__device__ __forceinline__ std::uint32_t tf32Round(float value) {
+    std::uint32_t bits;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(value));
+    return bits;
+}
+
+// value = hi + lo (+ a remainder below 2^-22 |value|), both TF32.
+__device__ __forceinline__ void splitTf32(float value, std::uint32_t& hi, std::uint32_t& lo) {
+    hi = tf32Round(value);
+    lo = tf32Round(value - __uint_as_float(hi));
+}
+
+// Element-wise tail of writeRowSegment for outputs that cannot take 128-bit stores.
+__device__ __noinline__ void writeRowSegmentSlow(float* out, std::int64_t out_row_stride, std::int64_t out_col_stride,
+                                                 const float* c, std::int64_t c_row_stride, std::int64_t c_col_stride,
+                                                 float scale, float beta, std::uint32_t row, std::uint32_t col,
+                                                 std::uint32_t n, const float* sum) {
+    for (std::uint32_t j = 0; j < 16 && col + j < n; ++j) {
+        float value = scale * sum[j];
+        if (c != nullptr) {
+            value += beta * c[static_cast<std::int64_t>(row) * c_row_stride + static_cast<std::int64_t>(col + j) * c_col_stride];
+        }
+        out[static_cast<std::int64_t>(row) * out_row_stride + static_cast<std::int64_t>(col + j) * out_col_stride] = value;
+    }
+}
+
+// Writes one row segment of 16 consecutive columns held by one thread.
+__device__ __forceinline__ void writeRowSegment(const TensorParams& p, const WorkItem& w, std::uint32_t row,
+                                                std::uint32_t col, const float (&sum)[16], bool vector_ok) {
+    if (row >= p.m || col >= p.n) { return; }
+    const bool partial = p.partials != nullptr;
+    float* out         = partial ? p.partials + static_cast<std::uint64_t>(w.split) * p.m * p.n : p.d;
+    const std::int64_t out_row_stride = partial ? p.n : p.d_row_stride;
+    const std::int64_t out_col_stride = partial ? 1 : p.d_col_stride;
+    const bool with_c                 = !partial && p.c != nullptr;
+    const float scale                 = partial ? 1.0F : p.alpha;
+    if (vector_ok) {
+        float* out_row     = out + static_cast<std::int64_t>(row) * out_row_stride + col;
+        const float* c_row = with_c ? p.c + static_cast<std::int64_t>(row) * p.c_row_stride + col : nullptr;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (col + q * 4 >= p.n) { continue; }
+            float4 value = make_float4(scale * sum[q * 4 + 0], scale * sum[q * 4 + 1], scale * sum[q * 4 + 2],
+                                       scale * sum[q * 4 + 3]);
+            if (with_c) {
+                const float4 addend = *reinterpret_cast<const float4*>(c_row + q * 4);
+                value.x += p.beta * addend.x;
+                value.y += p.beta * addend.y;
+                value.z += p.beta * addend.z;
+                value.w += p.beta * addend.w;
+            }
+            *reinterpret_cast<float4*>(out_row + q * 4) = value;
+        }
+        return;
+    }
+    // Any strides, any alignment: handed to an out-of-line routine through a
+    // local copy, so that the common path keeps `sum` in registers.
+    float copy[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { copy[j] = sum[j]; }
+    writeRowSegmentSlow(out, out_row_stride, out_col_stride, with_c ? p.c : nullptr, p.c_row_stride, p.c_col_stride,
+                        scale, p.beta, row, col, p.n, copy);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const TensorParams p, const std::uint32_t num_items) {
+    extern __shared__ unsigned char smem_raw[];
+    const std::uint32_t align_offset = (1024 - (smemAddress(smem_raw) & 1023)) & 1023;
+    unsigned char* smem              = smem_raw + align_offset;
+    Barriers* bars                   = reinterpret_cast<Barriers*>(smem + kBarrierOffset);
+    volatile int* abort_flag         = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarrierInit(&bars->a_full[s], 1);
+            mbarrierInit(&bars->mma_done[s], 1);
+            mbarrierInit(&bars->conv_done[s], 4);
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbarrierInit(&bars->raw_full[h], 1);
+            mbarrierInit(&bars->raw_empty[h], 4);
+        }
+        mbarrierInit(&bars->acc_full, 1);
+        mbarrierInit(&bars->acc_empty, 8);
+        mbarrierInit(&bars->flush, 1);
+        bars->abort_flag = 0;
+        fenceBarrierInit();
+        prefetchTensorMap(&map_a);
+        prefetchTensorMap(&map_b);
+    }
+    if (warp == kMmaWarp) { tmemAllocate(&bars->tmem_base, kTmemColumns); }
+    tcgen05FenceBeforeSync();
+    __syncthreads();
+    tcgen05FenceAfterSync();
+    const std::uint32_t tmem_base = bars->tmem_base;
+
+    // The producer and MMA warps walk their loops with all 32 lanes (so the
+    // warp stays converged for the block-wide barrier at the end); lane 0 alone
+    // issues copies, MMAs and commits.
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------ producer
+        std::uint32_t it = 0;  // K blocks issued so far, over all items
+        bool ok          = true;
+        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const WorkItem w = decodeItem(p, item);
+            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
+                const std::uint32_t s      = it % kStages;
+                const std::uint32_t use    = it / kStages;
+                unsigned char* stage       = smem + s * kStageBytes;
+                const std::int32_t k_coord = static_cast<std::int32_t>(w.k_begin + kb * kTileK);
+                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->mma_done[s], (use & 1) ^ 1, abort_flag));
+                if (!ok) { break; }
+                if (lane == 0) {
+                    mbarrierArriveExpectTx(&bars->a_full[s], kTileM * kTileK * 4);
+                    tmaLoad2d(stage + kAHiOffset, &map_a, &bars->a_full[s], k_coord, static_cast<std::int32_t>(w.tile_m));
+                }
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->raw_empty[h], (it & 1) ^ 1, abort_flag));
+                    if (!ok) { break; }
+                    if (lane == 0) {
+                        unsigned char* slot = smem + kRawOffset + h * kRawSlotBytes;
+                        mbarrierArriveExpectTx(&bars->raw_full[h], kRawSlotBytes);
+                        for (int q = 0; q < 4; ++q) {
+                            tmaLoad2d(slot + q * 4096, &map_b, &bars->raw_full[h],
+                                      static_cast<std::int32_t>(w.tile_n + h * 128 + q * 32), k_coord);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if (!ok) { *abort_flag = 1; }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr std::uint32_t kInstruction = umaInstructionTf32(kTileM, kTileN);
+        std::uint32_t it     = 0;
+        std::uint32_t chunks = 0;  // chunks started so far, over all items
+        bool ok              = true;
+        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const WorkItem w = decodeItem(p, item);
+            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
+                const bool chunk_start = kb % p.chunk_k_blocks == 0;
+                if (chunk_start) {
+                    // The drain warps must have emptied the chunk accumulator.
+                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag));
+                    if (!ok) { break; }
+                    ++chunks;
+                }
+                const std::uint32_t s   = it % kStages;
+                const std::uint32_t use = it / kStages;
+                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->conv_done[s], use & 1, abort_flag));
+                if (!ok) { break; }
+                tcgen05FenceAfterSync();
+                if (lane == 0) {
+                    const std::uint32_t stage = smemAddress(smem + s * kStageBytes);
+                    const std::uint64_t a_hi  = umaDescriptorK128(stage + kAHiOffset);
+                    const std::uint64_t a_lo  = umaDescriptorK128(stage + kALoOffset);
+                    const std::uint64_t b_hi  = umaDescriptorK128(stage + kBHiOffset);
+                    const std::uint64_t b_lo  = umaDescriptorK128(stage + kBLoOffset);
+#pragma unroll
+                    for (int step = 0; step < kTileK / 8; ++step) {
+                        // 8 TF32 elements = 32 bytes further along K: +2 in
+                        // the descriptor's 16-byte address units.
+                        const std::uint64_t advance = static_cast<std::uint64_t>(step * 2);
+                        const std::uint32_t fresh   = (chunk_start && step == 0) ? 0U : 1U;
+                        umaTf32(tmem_base, a_lo + advance, b_hi + advance, kInstruction, fresh);
+                        umaTf32(tmem_base, a_hi + advance, b_lo + advance, kInstruction, 1U);
+                        umaTf32(tmem_base, a_hi + advance, b_hi + advance, kInstruction, 1U);
+                    }
+                    umaCommit(&bars->mma_done[s]);
+                    const bool chunk_end = (kb + 1) % p.chunk_k_blocks == 0 || kb + 1 == w.k_blocks;
+                    if (chunk_end) { umaCommit(&bars->acc_full); }
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            // Let MMAs already issued finish before tensor memory is freed.
+            if (lane == 0) {
+                umaCommit(&bars->flush);
+                int never = 0;
+                mbarrierWait(&bars->flush, 0, &never);
+            }
+            __syncwarp();
+        }
+    } else if (warp >= kFirstConverter && warp < kFirstEpilogue) {
+        // ------------------------------------------------------------ converters
+        const int cw        = warp - kFirstConverter;            // 0..3, also the B box this warp owns
+        const int t         = threadIdx.x - kFirstConverter * 32;  // 0..127
+        std::uint32_t it    = 0;
+        bool ok             = true;
+        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const WorkItem w = decodeItem(p, item);
+            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
+                const std::uint32_t s   = it % kStages;
+                const std::uint32_t use = it / kStages;
+                unsigned char* stage    = smem + s * kStageBytes;
+                ok = mbarrierWait(&bars->a_full[s], use & 1, abort_flag);
+                if (!ok) { break; }
+                // A: elementwise, in place for the high part.
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int offset = (t + 128 * e) * 16;
+                    const float4 raw = *reinterpret_cast<const float4*>(stage + kAHiOffset + offset);
+                    uint4 hi, lo;
+                    splitTf32(raw.x, hi.x, lo.x);
+                    splitTf32(raw.y, hi.y, lo.y);
+                    splitTf32(raw.z, hi.z, lo.z);
+                    splitTf32(raw.w, hi.w, lo.w);
+                    *reinterpret_cast<uint4*>(stage + kAHiOffset + offset) = hi;
+                    *reinterpret_cast<uint4*>(stage + kALoOffset + offset) = lo;
+                }
+                // B: lane = k. A 128-bit read takes 4 consecutive n at one k from
+                // the raw box (rows of 128 bytes indexed by k, 16-byte chunks
+                // XOR-swizzled by k % 8); four 32-bit writes put them into rows
+                // n of the K-major tile (16-byte chunks XOR-swizzled by n % 8).
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = mbarrierWait(&bars->raw_full[h], it & 1, abort_flag);
+                    if (!ok) { break; }
+                    const unsigned char* box = smem + kRawOffset + h * kRawSlotBytes + cw * 4096;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 raw = *reinterpret_cast<const float4*>(box + lane * 128 + ((c ^ (lane & 7)) << 4));
+                        const float values[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int n_row = h * 128 + cw * 32 + c * 4 + j;
+                            const int dst   = n_row * 128 + (((lane >> 2) ^ (n_row & 7)) << 4) + (lane & 3) * 4;
+                            std::uint32_t hi, lo;
+                            splitTf32(values[j], hi, lo);
+                            *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
+                            *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) { mbarrierArrive(&bars->raw_empty[h]); }
+                }
+                if (!ok) { break; }
+                // Publish the stage to the tensor core (async proxy).
+                fenceProxyAsync();
+                __syncwarp();
+                if (lane == 0) { mbarrierArrive(&bars->conv_done[s]); }
+            }
+        }
+        if (!ok) { *abort_flag = 1; }
+    } else if (warp >= kFirstEpilogue) {
+        // ------------------------------------------------------------ drain / epilogue
+        const int e                   = warp - kFirstEpilogue;  // 0..7
+        const std::uint32_t lane_base = static_cast<std::uint32_t>(32 * (e & 3));
+        const std::uint32_t col_half  = static_cast<std::uint32_t>(128 * (e >> 2));
+        const std::uint32_t tmem_row  = tmem_base + (lane_base << 16);
+        std::uint32_t chunks          = 0;
+        bool ok                       = true;
+        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            const WorkItem w               = decodeItem(p, item);
+            const std::uint32_t num_chunks = (w.k_blocks + p.chunk_k_blocks - 1) / p.chunk_k_blocks;
+            const std::uint32_t row        = w.tile_m + lane_base + lane;
+            const bool partial             = p.partials != nullptr;
+            const float* out_base = partial ? p.partials + static_cast<std::uint64_t>(w.split) * p.m * p.n : p.d;
+            const bool vector_ok =
+                (p.n & 3) == 0 && (reinterpret_cast<std::uintptr_t>(out_base) & 15) == 0 &&
+                (partial || (p.d_col_stride == 1 && (p.d_row_stride & 3) == 0)) &&
+                (partial || p.c == nullptr ||
+                 (p.c_col_stride == 1 && (p.c_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(p.c) & 15) == 0));
+            for (std::uint32_t chunk = 0; chunk < num_chunks && ok; ++chunk, ++chunks) {
+                ok = mbarrierWait(&bars->acc_full, chunks & 1, abort_flag);
+                if (!ok) { break; }
+                tcgen05FenceAfterSync();
+                const bool first = chunk == 0;
+                const bool last  = chunk + 1 == num_chunks;
+                if (last) {
+                    // Piece by piece: fold in the running sum and write out. The
+                    // chunk accumulator is released as soon as its last piece
+                    // has been read, before that piece is written.
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece) {
+                        float sum[16];
+                        tmemLoad16(tmem_row + col_half + piece * 16, sum);
+                        if (!first) {
+                            float running[16];
+                            tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
+                        }
+                        if (piece == 7) {
+                            tcgen05FenceBeforeSync();
+                            __syncwarp();
+                            if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
+                        }
+                        writeRowSegment(p, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
+                    }
+                } else {
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece) {
+                        float sum[16];
+                        tmemLoad16(tmem_row + col_half + piece * 16, sum);
+                        if (!first) {
+                            float running[16];
+                            tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
+                        }
+                        tmemStore16(tmem_row + kRunningColumn + col_half + piece * 16, sum);
+                    }
+                    tcgen05FenceBeforeSync();
+                    __syncwarp();
+                    if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
+                }
+            }
+        }
+        if (!ok) { *abort_flag = 1; }
+    }
+
+    __syncthreads();
+    if (*abort_flag != 0) {
+        if (threadIdx.x == 0) {
+            if (p.status != nullptr) { *p.status = 2; }
+            // Copies that were armed but never consumed may still be landing.
+            int never = 0;
+            for (int s = 0; s < kStages; ++s) {
+                mbarrierWait(&bars->a_full[s], 0, &never);
+                mbarrierWait(&bars->a_full[s], 1, &never);
+            }
+            for (int h = 0; h < 2; ++h) {
+                mbarrierWait(&bars->raw_full[h], 0, &never);
+                mbarrierWait(&bars->raw_full[h], 1, &never);
+            }
+        }
+        __syncthreads();
+    }
+    if (warp == kMmaWarp) {
+        tcgen05FenceAfterSync();
+        tmemFree(tmem_base, kTmemColumns);
+    }
+}
+
+// Number of K slices that fills the SMs in whole waves: the smallest count
+// whose last wave is at least 90 % full, bounded by the slice length.
+std::uint32_t chooseSplits(std::uint64_t tiles, std::uint64_t k, int sms) {
+    const std::uint64_t most = k / 1024 < 2 ? 2 : k / 1024;  // slices of >= 1024
+    std::uint32_t best       = 2;
+    double best_fill         = 0.0;
+    for (std::uint64_t s = 2; s <= most && s <= 128; ++s) {
+        const std::uint64_t items = tiles * s;
+        const std::uint64_t waves = ceilDiv(items, static_cast<std::uint64_t>(sms));
+        const double fill         = static_cast<double>(items) / static_cast<double>(waves * sms);
+        if (fill > best_fill + 1e-9) {
+            best_fill = fill;
+            best      = static_cast<std::uint32_t>(s);
+        }
+        if (fill >= 0.90 && waves >= 2) { return static_cast<std::uint32_t>(s); }
+    }
+    return best;
+}
+
+}  // namespace
+
+const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
+    if (desc.m * desc.n == 0 || desc.k == 0) { return "the problem is empty"; }
+    if (desc.m >= (1ULL << 31) || desc.n >= (1ULL << 31) || desc.k >= (1ULL << 31)) {
+        return "an extent does not fit 31 bits";
+    }
+    if (desc.k < 32) { return "K is shorter than one K block"; }
+    if (!tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m)) {
+        return "A is not row-major with a 16-byte aligned base and row pitch";
+    }
+    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k)) {
+        return "B is not row-major with a 16-byte aligned base and row pitch";
+    }
+    if (ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN) >= (1ULL << 24)) { return "too many output tiles"; }
+    if (split_k && desc.k < 2048) { return "K is too short to split"; }
+    return nullptr;
+}
+
+int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t capacity) {
+    const FtcudaGemmDesc& desc = state.desc;
+    int sms                    = 0;
+    if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
+    if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
+    state.variant              = kVariantTmaAk;
+    const std::uint64_t tiles  = ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
+    state.splits               = 1;
+    state.k_per_split          = static_cast<std::uint32_t>(ceilDiv(desc.k, kTileK) * kTileK);
+    if (split_k) {
+        const std::uint32_t wanted = chooseSplits(tiles, desc.k, sms);
+        state.k_per_split = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, wanted), kTileK) * kTileK);
+        state.splits      = static_cast<std::uint32_t>(ceilDiv(desc.k, state.k_per_split));
+    }
+    const std::uint64_t items = tiles * state.splits;
+    state.grid_x              = static_cast<std::uint32_t>(items < static_cast<std::uint64_t>(sms) ? items : sms);
+    state.grid_y              = 1;
+    state.grid_z              = 1;
+    state.block               = kThreads;
+    state.smem_bytes          = kSmemBytes;
+    state.chunk_k_blocks      = 8;  // 256 K elements between drains
+    state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
+    if (!encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
+                           static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float), kTileK, kTileM, true, message,
+                           capacity)) {
+        return 1;
+    }
+    if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
+                           static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), 32, kTileK, true, message,
+                           capacity)) {
+        return 1;
+    }
+    const cudaError_t error =
+        cudaFuncSetAttribute(tensorGemm3xTf32, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (error != cudaSuccess) {
+        return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error));
+    }
+    return 0;
+}
+
+cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream) {
+    const FtcudaGemmDesc& desc = state.desc;
+    TensorParams p{};
+    p.c              = desc.c;
+    p.d              = desc.d;
+    p.c_row_stride   = desc.c_row_stride;
+    p.c_col_stride   = desc.c_col_stride;
+    p.d_row_stride   = desc.d_row_stride;
+    p.d_col_stride   = desc.d_col_stride;
+    p.m              = static_cast<std::uint32_t>(desc.m);
+    p.n              = static_cast<std::uint32_t>(desc.n);
+    p.k              = static_cast<std::uint32_t>(desc.k);
+    p.tiles_m        = static_cast<std::uint32_t>(ceilDiv(desc.m, kTileM));
+    p.tiles_n        = static_cast<std::uint32_t>(ceilDiv(desc.n, kTileN));
+    p.splits         = state.splits;
+    p.k_per_split    = state.k_per_split;
+    p.chunk_k_blocks = state.chunk_k_blocks;
+    p.alpha          = desc.alpha;
+    p.beta           = desc.beta;
+    p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
+    p.status         = state.device_status;
+    const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
+    tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+    cudaError_t error      = cudaGetLastError();
+    std::uint64_t launches = 1;
+    if (error == cudaSuccess && state.splits > 1) {
+        error = launchSplitKReduce(desc, static_cast<const float*>(workspace), state.splits, stream);
+        ++launches;
+    }
+    countLaunches(launches);
+    return error;
+}
+
+}  // namespace ftcuda

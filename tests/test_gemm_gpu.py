@@ -1,0 +1,322 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU
+oracle, the committed golden vectors and a float64 reference.
+
+Tolerances
+  * exact-FP32 kernels vs the oracle: the reference's own criterion,
+    |d - ref| <= 2e-5 + 2e-5 |ref| (tests/api/gemm_numerics_test.cpp:55-59 there).
+  * every kernel vs float64: scaled error
+        max |d - d64| / (||a_row|| * ||b_col|| + |beta c|)
+    at most 2x that of torch's FP32 matmul on the same inputs (with a floor of
+    2^-24 so that a lucky torch result on a tiny case cannot fail the test).
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).parent / "golden"
+GRID = [(1, 1, 1), (3, 4, 2), (16, 16, 16), (64, 48, 32), (129, 65, 17), (33, 257, 65), (256, 128, 64)]
+ERROR_FLOOR = 2.0 ** -24
+
+
+@pytest.fixture(scope="module")
+def gpu(capi):
+    if not torch.cuda.is_available():
+        pytest.fail("the GPU tests need a CUDA device")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    import gpu_support
+
+    return gpu_support
+
+
+def platform_gemm(capi, gpu, kernel, a, b, c, alpha, beta, d=None):
+    """Runs one kernel family through ftcuda_gemm_configure / ftcuda_gemm_launch."""
+    m, n = a.shape[0], b.shape[1]
+    if d is None:
+        d = torch.full((m, n), float("nan"), device="cuda")
+    c_operand = gpu.operand(c) if c is not None else capi.null_operand(m, n)
+    desc = capi.make_desc(gpu.operand(a), gpu.operand(b), c_operand, gpu.operand(d), alpha, beta,
+                          torch.cuda.current_device())
+    reason = capi.platform_supports(kernel, desc)
+    if reason is not None:
+        return None, reason
+    launch = capi.PlatformGemm(kernel, desc)
+    workspace = torch.empty(max(launch.workspace_bytes, 1), dtype=torch.uint8, device="cuda")
+    launch.run(workspace.data_ptr(), launch.workspace_bytes, gpu.current_stream())
+    torch.cuda.synchronize()
+    return d, None
+
+
+def check_against_float64(oracle, d, a, b, c, alpha, beta, what):
+    exact = alpha * (a.double() @ b.double())
+    if c is not None:
+        exact = exact + beta * c.double()
+    plain = alpha * (a @ b)
+    if c is not None:
+        plain = plain + beta * c
+    # alpha scales both the numerator and the row norms' product.
+    ours = oracle.scaled_error(d, exact, a * abs(alpha), b, c, beta)
+    torch_error = oracle.scaled_error(plain, exact, a * abs(alpha), b, c, beta)
+    assert torch.isfinite(d).all(), f"{what}: non-finite output"
+    assert ours <= 2.0 * max(torch_error, ERROR_FLOOR), f"{what}: scaled error {ours:.3e} vs torch FP32 {torch_error:.3e}"
+    return ours, torch_error
+
+
+# --------------------------------------------------------------- golden vectors
+
+def test_known_answer_one_shot(capi, gpu):
+    # tests/api/gemm_api_test.cpp:392-438 of the reference: exact equality.
+    a = torch.tensor([[1.0, 2.0], [3.0, 4.0]], device="cuda")
+    b = torch.tensor([[5.0, 6.0], [7.0, 8.0]], device="cuda")
+    c = torch.zeros(2, 2, device="cuda")
+    d = torch.empty(2, 2, device="cuda")
+    capi.gemm_once(gpu.operand(a), gpu.operand(b), gpu.operand(c), gpu.operand(d), 2.0, 0.5, stream=gpu.current_stream())
+    torch.cuda.synchronize()
+    assert d.cpu().tolist() == [[38.0, 44.0], [86.0, 100.0]]
+    assert capi.last_status() == capi.STATUS_SUCCESS and capi.last_message() == ""
+
+
+@pytest.mark.parametrize("shape", GRID, ids=lambda s: "x".join(map(str, s)))
+def test_reference_grid_selected_primitive(capi, gpu, oracle, shape):
+    """The reference's numerics test, run as it runs it: staged API, primitive 0."""
+    m, k, n = shape
+    golden = np.load(GOLDEN / "reference_grid.npz")
+    a_h, b_h, c_h = oracle.grid_inputs(m, k, n)
+    a, b, c = (torch.from_numpy(x).cuda() for x in (a_h, b_h, c_h))
+    fresh, names = gpu.gemm(a, b, None, 1.5, 0.0)
+    assert names[-1] == "Fp32Gemm"
+    ok, ratio = oracle.within_reference_tolerance(fresh.cpu().numpy(), golden[f"fresh_{m}x{k}x{n}"])
+    assert ok, f"fresh {names[0]}: worst ratio {ratio}"
+    accumulated, _ = gpu.gemm(a, b, c, 1.5, 1.25)
+    ok, ratio = oracle.within_reference_tolerance(accumulated.cpu().numpy(), golden[f"accumulated_{m}x{k}x{n}"])
+    assert ok, f"accumulated {names[0]}: worst ratio {ratio}"
+
+
+@pytest.mark.parametrize("kernel", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("shape", GRID + [(128, 64, 96), (255, 512, 260), (17, 2304, 64), (384, 4100, 516)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_every_kernel_family_against_oracle(capi, gpu, oracle, kernel, shape):
+    m, k, n = shape
+    a_h, b_h, c_h = oracle.grid_inputs(m, k, n)
+    a, b, c = (torch.from_numpy(x).cuda() for x in (a_h, b_h, c_h))
+    d, reason = platform_gemm(capi, gpu, kernel, a, b, c, 1.5, 1.25)
+    if d is None:
+        pytest.skip(f"{capi.KERNEL_NAMES[kernel]} declines {shape}: {reason}")
+    expected = oracle.host_gemm(a_h, b_h, c_h, 1.5, 1.25, fma=True)
+    # K up to 4100 here: the sequential-sum rounding of the oracle itself grows
+    # with K, so the absolute part of the reference's tolerance is scaled by
+    # sqrt(K / 257) beyond the reference grid's largest K.
+    slack = max(1.0, (k / 257.0) ** 0.5)
+    ok, ratio = oracle.within_reference_tolerance(d.cpu().numpy(), expected, 2e-5 * slack, 2e-5 * slack)
+    assert ok, f"{capi.KERNEL_NAMES[kernel]} {shape}: worst ratio {ratio}"
+    # No C: beta must not matter and C must not be read.
+    d, _ = platform_gemm(capi, gpu, kernel, a, b, None, -2.0, 7.0)
+    expected = oracle.host_gemm(a_h, b_h, None, -2.0, 7.0, fma=True)
+    ok, ratio = oracle.within_reference_tolerance(d.cpu().numpy(), expected, 2e-5 * slack, 2e-5 * slack)
+    assert ok, f"{capi.KERNEL_NAMES[kernel]} {shape} without C: worst ratio {ratio}"
+
+
+# --------------------------------------------------------------- API behaviour on a device
+
+def test_rebinding_and_plan_outlives_args(capi, gpu):
+    # tests/api/gemm_api_test.cpp:22-138 of the reference: 3x2x4, two data sets, negative beta.
+    torch.manual_seed(11)
+    a1, b1, c1 = torch.randn(3, 2, device="cuda"), torch.randn(2, 4, device="cuda"), torch.randn(3, 4, device="cuda")
+    a2, b2, c2 = torch.randn(3, 2, device="cuda"), torch.randn(2, 4, device="cuda"), torch.randn(3, 4, device="cuda")
+    d1, d2 = torch.empty(3, 4, device="cuda"), torch.empty(3, 4, device="cuda")
+    plan1 = gpu.make_plan(a1, b1, c1, d1, 1.25, -0.5)
+    plan2 = gpu.make_plan(a2, b2, c2, d2, -2.0, 0.75)
+    assert plan1.handle.value != plan2.handle.value
+    gpu.run_plan(plan2)
+    gpu.run_plan(plan1)
+    torch.cuda.synchronize()
+    assert torch.allclose(d1, 1.25 * (a1 @ b1) - 0.5 * c1, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(d2, -2.0 * (a2 @ b2) + 0.75 * c2, rtol=1e-5, atol=1e-5)
+
+
+def test_in_place_accumulation(capi, gpu):
+    # tests/api/gemm_api_test.cpp:330-390: C and D are the same buffer, alpha 2, beta 3.
+    torch.manual_seed(12)
+    for kernel, shape in ((0, (3, 2, 4)), (0, (200, 96, 136)), (1, (256, 128, 512)), (3, (4, 512, 64))):
+        m, k, n = shape
+        a, b, cd = torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda"), torch.randn(m, n, device="cuda")
+        expected = 2.0 * (a.double() @ b.double()) + 3.0 * cd.double()
+        d, reason = platform_gemm(capi, gpu, kernel, a, b, cd, 2.0, 3.0, d=cd)
+        assert d is not None, reason
+        assert torch.allclose(cd.double(), expected, rtol=1e-4, atol=1e-3), capi.KERNEL_NAMES[kernel]
+
+
+def test_empty_output_and_zero_depth(capi, gpu):
+    # Empty output: succeeds with no storage at all (gemm_api_test.cpp:140-165).
+    plan = gpu.binding().make_plan(capi.null_operand(0, 5), capi.null_operand(5, 7), capi.null_operand(0, 7),
+                                   capi.null_operand(0, 7), 1.0, 0.0)
+    assert plan.num_primitives >= 1 and plan.workspace_bytes(0) == 0
+    plan.execute(0, 0, 0, gpu.current_stream())
+    # K == 0 with null A and B: D = beta * C (fp32_gemm_test.cpp:138-145, fp32_gemm.cpp:57-60).
+    c = torch.randn(6, 9, device="cuda")
+    d = torch.empty(6, 9, device="cuda")
+    plan = gpu.binding().make_plan(capi.null_operand(6, 0), capi.null_operand(0, 9), gpu.operand(c), gpu.operand(d),
+                                   3.0, 0.5)
+    gpu.run_plan(plan)
+    torch.cuda.synchronize()
+    assert torch.equal(d, 0.5 * c)
+
+
+def test_status_codes(capi, gpu):
+    b = gpu.binding()
+    a_t, b_t = torch.zeros(4, 3, device="cuda"), torch.zeros(3, 5, device="cuda")
+    c_t, d_t = torch.zeros(4, 5, device="cuda"), torch.zeros(4, 5, device="cuda")
+    op = gpu.operand
+    # Shape mismatch -> INVALID_ARGUMENT (gemm_api_test.cpp:186-250).
+    with pytest.raises(capi.FTrainError) as info:
+        b.make_plan(op(a_t), op(torch.zeros(4, 5, device="cuda")), op(c_t), op(d_t))
+    assert info.value.status == capi.STATUS_INVALID_ARGUMENT
+    # INT64_MAX extents -> OVERFLOW (gemm_api_test.cpp:167-184).
+    big = 2 ** 63 - 1
+    with pytest.raises(capi.FTrainError) as info:
+        b.make_plan((0, (big, big), None), (0, (big, big), None), (0, (big, big), None), (0, (big, big), None))
+    assert info.value.status == capi.STATUS_OVERFLOW
+    # Null A with work to do -> UNSUPPORTED, naming the primitive (gemm_api_test.cpp:252-328).
+    with pytest.raises(capi.FTrainError) as info:
+        b.make_plan(capi.null_operand(4, 3), op(b_t), op(c_t), op(d_t))
+    assert info.value.status == capi.STATUS_UNSUPPORTED
+    assert "Fp32Gemm" in info.value.message and "a required operand address is null" in info.value.message
+    # FP16 A -> UNSUPPORTED "an operand is not fp32"; FP64 compute type -> UNSUPPORTED.
+    args = capi.Args(b.ops)
+    keep = []
+    for name, tensor, numeric in (("a", a_t, capi.NUMERIC_FP16), ("b", b_t, capi.NUMERIC_FP32),
+                                  ("c", c_t, capi.NUMERIC_FP32), ("d", d_t, capi.NUMERIC_FP32)):
+        view, alive = capi.make_view(tensor.data_ptr(), tensor.shape, numeric_type=numeric)
+        keep.append(alive)
+        args.set_tensor(b.roles[name], view)
+    import ctypes
+
+    scalar = ctypes.c_float(1.0)
+    for name in ("alpha", "beta"):
+        view, alive = capi.make_view(ctypes.addressof(scalar), (), host=True)
+        keep.append(alive)
+        args.set_tensor(b.roles[name], view)
+    args.set_gemm(b.gemm, capi.NUMERIC_FP32)
+    with pytest.raises(capi.FTrainError) as info:
+        capi.Plan(args)
+    assert info.value.status == capi.STATUS_UNSUPPORTED
+    assert "Fp32Gemm" in info.value.message and "an operand is not fp32" in info.value.message
+    view, alive = capi.make_view(a_t.data_ptr(), a_t.shape)
+    args.set_tensor(b.roles["a"], view)
+    args.set_gemm(b.gemm, capi.NUMERIC_FP64)
+    with pytest.raises(capi.FTrainError) as info:
+        capi.Plan(args)
+    assert info.value.status == capi.STATUS_UNSUPPORTED and "compute type is not fp32" in info.value.message
+    # Workspace too small / bad index -> INVALID_ARGUMENT without dispatch.
+    plan = b.make_plan(op(a_t), op(b_t), op(c_t), op(d_t))
+    with pytest.raises(capi.FTrainError) as info:
+        plan.execute(plan.num_primitives, 0, 0, gpu.current_stream())
+    assert info.value.status == capi.STATUS_INVALID_ARGUMENT
+
+
+def test_selection_cache_and_workspace_walk(capi, gpu):
+    # Tall K with few tiles: the split-K kernel is recommended and asks for a
+    # workspace; a later index needs none (usage: walk indices by budget).
+    a, b = torch.randn(256, 16384, device="cuda"), torch.randn(16384, 256, device="cuda")
+    d = torch.empty(256, 256, device="cuda")
+    plan = gpu.make_plan(a, b, None, d)
+    names = plan.primitive_names()
+    assert names[0] == "Fp32Gemm3xTf32SplitK" and plan.workspace_bytes(0) > 0
+    assert names[-1] == "Fp32Gemm" and plan.workspace_bytes(len(names) - 1) == 0
+    with pytest.raises(capi.FTrainError) as info:
+        plan.execute(0, 0, 0, gpu.current_stream())
+    assert info.value.status == capi.STATUS_INVALID_ARGUMENT
+    # Same problem description, other addresses: same ordered selection (cache hit).
+    a2, b2, d2 = a.clone(), b.clone(), torch.empty_like(d)
+    again = gpu.make_plan(a2, b2, None, d2)
+    assert again.primitive_names() == names and again.handle.value != plan.handle.value
+    exact = a.double() @ b.double()
+    for index in range(len(names)):
+        d.fill_(float("nan"))
+        gpu.run_plan(plan, index)
+        torch.cuda.synchronize()
+        assert torch.allclose(d.double(), exact, rtol=1e-4, atol=2e-2), names[index]
+
+
+# --------------------------------------------------------------- BASELINE configurations
+
+def test_config1_small_default(capi, gpu, oracle):
+    golden = np.load(GOLDEN / "torch_config1.npz")
+    a, b = torch.from_numpy(golden["a"]).cuda(), torch.from_numpy(golden["b"]).cuda()
+    d, names = gpu.gemm(a, b)
+    error = oracle.scaled_error(d.cpu(), golden["d64"], golden["a"], golden["b"])
+    torch_error = oracle.scaled_error(golden["d32"], golden["d64"], golden["a"], golden["b"])
+    assert error <= 2.0 * max(torch_error, ERROR_FLOOR), (names, error, torch_error)
+
+
+def test_config2_4096_cubed_with_addend(capi, gpu, oracle):
+    torch.manual_seed(1)
+    a, b, c = (torch.randn(4096, 4096, device="cuda") for _ in range(3))
+    report = {}
+    for kernel in (0, 1):
+        d, reason = platform_gemm(capi, gpu, kernel, a, b, c, 1.5, 0.5)
+        assert d is not None, reason
+        report[capi.KERNEL_NAMES[kernel]] = check_against_float64(oracle, d, a, b, c, 1.5, 0.5, capi.KERNEL_NAMES[kernel])
+    print("config2 scaled errors (ours, torch fp32):", report)
+
+
+@pytest.mark.parametrize("m", [1, 17, 255, 4097])
+def test_config3_tail_sweep_contiguous_and_transposed(capi, gpu, oracle, m):
+    k = n = 4096
+    generator = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.rand(m, k, device="cuda", generator=generator) * 2 - 1
+    b = torch.rand(k, n, device="cuda", generator=generator) * 2 - 1
+    buffer = a.t().contiguous()  # k x m; its transpose is an (m, k) view with strides (1, m)
+    for label, a_view in (("contiguous", a), ("transposed view", buffer.t())):
+        d, names = gpu.gemm(a_view, b)
+        check_against_float64(oracle, d, a, b, None, 1.0, 0.0, f"m={m} {label} via {names[0]}")
+        # A second Plan for the same description reproduces the selection.
+        assert gpu.make_plan(a_view, b, None, d).primitive_names() == names
+    if m <= 17:
+        assert gpu.make_plan(a, b, None, d).primitive_name(0) == "Fp32GemmSkinny"
+
+
+def test_config4_training_shape_rows_sampled(capi, gpu, oracle):
+    m, k, n = 16384, 4096, 14336
+    torch.manual_seed(3)
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(k, n, device="cuda") / (k ** 0.5)
+    d, names = gpu.gemm(a, b)
+    assert names[0] == "Fp32Gemm3xTf32"
+    rows = torch.tensor([0, 1, 127, 128, 4095, 8191, 8192, 16383], device="cuda")
+    check_against_float64(oracle, d[rows], a[rows], b, None, 1.0, 0.0, "config 4 sampled rows")
+    # Whole-matrix property: D @ ones == A @ (B @ ones) up to rounding.
+    ones = torch.ones(n, 1, device="cuda", dtype=torch.float64)
+    lhs = d.double() @ ones
+    rhs = a.double() @ (b.double() @ ones)
+    assert torch.allclose(lhs, rhs, rtol=1e-6, atol=1e-3)
+
+
+def test_config5_tall_k_split(capi, gpu, oracle):
+    m = n = 2048
+    k = 262144
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    a = torch.rand(m, k, device="cuda", generator=generator) * 2 - 1
+    b = torch.rand(k, n, device="cuda", generator=generator) * 2 - 1
+    d, names = gpu.gemm(a, b)
+    assert names[0] == "Fp32Gemm3xTf32SplitK"
+    rows = torch.tensor([0, 5, 1023, 2047], device="cuda")
+    check_against_float64(oracle, d[rows], a[rows], b, None, 1.0, 0.0, "config 5 sampled rows")
+
+
+def test_plan_reuse_many_executions(capi, gpu):
+    a, b = torch.randn(1024, 1024, device="cuda"), torch.randn(1024, 1024, device="cuda")
+    d = torch.empty(1024, 1024, device="cuda")
+    plan = gpu.make_plan(a, b, None, d)
+    size = plan.workspace_bytes(0)
+    workspace = torch.empty(max(size, 1), dtype=torch.uint8, device="cuda")
+    stream = gpu.current_stream()
+    before = capi.launch_count()
+    for _ in range(1000):
+        plan.execute(0, workspace.data_ptr() if size else 0, size, stream)
+    torch.cuda.synchronize()
+    assert capi.launch_count() - before >= 1000
+    assert torch.allclose(d.double(), a.double() @ b.double(), rtol=1e-4, atol=1e-2)
