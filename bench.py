@@ -184,8 +184,24 @@ def run_reference_arm(options) -> int:
     return 0
 
 
+def plan_reuse_native(device_index: int) -> dict | None:
+    """The C++ harness (no binding cost): one Plan for m=n=k=1024, 1000 executes."""
+    binary = REPO / "flash-train_b200" / "python" / "flash_train" / "bin" / "plan_reuse_bench"
+    if not binary.exists():
+        return None
+    environment = dict(os.environ)
+    visible = environment.get("CUDA_VISIBLE_DEVICES")
+    devices = visible.split(",") if visible else None
+    environment["CUDA_VISIBLE_DEVICES"] = devices[device_index] if devices else str(device_index)
+    result = subprocess.run([str(binary), "1024", "1024", "1024", "1000", "0"], capture_output=True, text=True,
+                            env=environment, timeout=300)
+    if result.returncode != 0:
+        return {"error": result.stderr.strip()[-300:]}
+    return json.loads(result.stdout.strip().splitlines()[-1])
+
+
 def plan_reuse_overhead(capi, torch, device) -> dict:
-    """One Plan for m=n=k=1024, executed 1000 times: host microseconds per enqueue."""
+    """Same measurement through the Python ctypes binding (adds the binding's own call cost)."""
     from flash_train.capi import GemmBinding, null_operand, tensor_operand
 
     a = torch.randn(1024, 1024, device=device)
@@ -224,6 +240,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
+    parser.add_argument("--primitive", default=None,
+                        help="run this Primitive of the Plan instead of index 0 (per-primitive tier), e.g. Fp32Gemm")
     options = parser.parse_args()
     options.warmup = max(options.warmup, 3) if options.impl == "ours" else options.warmup
 
@@ -259,14 +277,15 @@ def main() -> int:
     plan = GemmBinding().make_plan(tensor_operand(a), tensor_operand(b),
                                    tensor_operand(c) if c is not None else null_operand(rows, n),
                                    tensor_operand(d), alpha, beta)
-    primitive = plan.primitive_name(0)
-    size = plan.workspace_bytes(0)
+    index = 0 if options.primitive is None else plan.index_of(options.primitive)
+    primitive = plan.primitive_name(index)
+    size = plan.workspace_bytes(index)
     workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
     pointer = workspace.data_ptr() if size else 0
     stream = torch.cuda.current_stream().cuda_stream
 
     def step():
-        plan.execute(0, pointer, size, stream)
+        plan.execute(index, pointer, size, stream)
 
     def barrier():
         if distributed:
@@ -358,14 +377,14 @@ def main() -> int:
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": options.workload, "m": m, "k": k, "n": n, "rows_per_gpu": rows,
                    "partition": "rows of A and D split across GPUs, B replicated, no communication",
-                   "primitive": primitive, "workspace_bytes": size,
+                   "primitive": primitive, "plan": plan.primitive_names(), "workspace_bytes": size,
                    "l2": "operands (A+B+D > 1 GB per GPU at N=1) exceed the 126 MB L2, so each step re-reads HBM"},
         "roofline": roofline, "clocks": clocks, "gpu_launches": launches,
     }
     if e2e is not None:
         line["e2e"] = e2e
     if not options.no_extras:
-        line["plan_reuse"] = plan_reuse_overhead(capi, torch, device)
+        line["plan_reuse"] = {"native": plan_reuse_native(local_rank), "python_ctypes": plan_reuse_overhead(capi, torch, device)}
         if world == 1:
             baseline = cpu_reference_run(options.workload, 3, 1)
             line["cpu_baseline"] = {key: baseline[key] for key in ("value", "unit", "cores", "kind", "sample")}

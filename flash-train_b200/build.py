@@ -7,6 +7,7 @@ Outputs (next to the Python package, the layout of the reference wheel,
 python/flash_train/torch/__init__.py:15-18 there):
   flash-train_b200/python/flash_train/libflash_train.so
   flash-train_b200/python/flash_train/torch/_flash_train_torch*.so
+  flash-train_b200/python/flash_train/bin/plan_reuse_bench
 
 Host C++ is compiled with g++, CUDA sources with nvcc for sm_100a only
 (-gencode arch=compute_100a,code=sm_100a); the CUDA runtime is linked
@@ -60,7 +61,7 @@ def _run(command: list[str]) -> None:
 
 
 def host_sources() -> list[Path]:
-    return sorted(p for p in CSRC.rglob("*.cpp") if "cuda" not in p.relative_to(CSRC).parts[:1])
+    return sorted(p for p in CSRC.rglob("*.cpp") if p.relative_to(CSRC).parts[0] not in ("cuda", "bench"))
 
 
 def cuda_sources() -> list[Path]:
@@ -103,6 +104,20 @@ def build_library(verbose: bool = True) -> Path:
     return target
 
 
+def build_plan_bench(verbose: bool = True) -> Path:
+    """bin/plan_reuse_bench: host cost of Plan reuse measured from C++ (no binding in the way)."""
+    library = build_library(verbose)
+    source = CSRC / "bench" / "plan_reuse_bench.cpp"
+    target = PACKAGE / "bin" / "plan_reuse_bench"
+    target.parent.mkdir(exist_ok=True)
+    if _stale(target, [source, library], _newest_header()):
+        _run([NVCC, "-std=c++17", "-O2", "-cudart", "static", f"-I{INCLUDE}", str(source), "-o", str(target),
+              f"-L{PACKAGE}", "-lflash_train", "-Xlinker", "-rpath,$ORIGIN/.."])
+        if verbose:
+            print(f"[build] built {target.relative_to(REPO)}", flush=True)
+    return target
+
+
 def build_torch_binding(verbose: bool = True) -> Path:
     """The pybind11 module behind flash_train.torch.gemm."""
     import torch
@@ -134,6 +149,7 @@ def main() -> int:
     parser.add_argument("--quiet", action="store_true")
     options = parser.parse_args()
     build_library(not options.quiet)
+    build_plan_bench(not options.quiet)
     if not options.no_torch:
         build_torch_binding(not options.quiet)
     return 0

@@ -34,6 +34,25 @@ const GemmEntry& gemmEntry() {
     return entry;
 }
 
+// The reference's one-shot call always runs primitive 0 and fails when the
+// caller's workspace is smaller than that primitive needs (src/api/gemm_api.cpp:73
+// there, where the only primitive needs none). Here primitive 0 can be a
+// split-K kernel that wants a workspace, so the one-shot call follows the
+// documented budget walk instead: the first primitive, in the Plan's best-first
+// order, whose requirement the supplied workspace covers. With a sufficient
+// workspace that is primitive 0, as in the reference; if nothing fits,
+// primitive 0 is run so that its diagnostic reaches the caller.
+std::uint64_t pickPrimitive(FTrainPlan plan, const void* workspace, std::uint64_t workspace_bytes) {
+    std::uint64_t count = 0;
+    if (ftrainPlanGetNumPrimitives(plan, &count) != FTRAIN_STATUS_SUCCESS) { return 0; }
+    for (std::uint64_t index = 0; index < count; ++index) {
+        std::uint64_t needed = 0;
+        if (ftrainPlanGetPrimitiveRequiredWorkspaceBytes(plan, index, &needed) != FTRAIN_STATUS_SUCCESS) { return 0; }
+        if (needed == 0 || (workspace != nullptr && needed <= workspace_bytes)) { return index; }
+    }
+    return 0;
+}
+
 }  // namespace
 
 extern "C" FTrainStatus ftrainGemm(FTrainStorageView a, FTrainStorageView b, FTrainStorageView c, FTrainStorageView d,
@@ -56,7 +75,8 @@ extern "C" FTrainStatus ftrainGemm(FTrainStorageView a, FTrainStorageView b, FTr
     if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainArgsSetGemm(args, entry.gemm, compute_type); }
     if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainPlanCreate(&plan, args); }
     if (status == FTRAIN_STATUS_SUCCESS) {
-        status = ftrainPlanExecutePrimitive(plan, 0, workspace, workspace_bytes, stream);
+        status = ftrainPlanExecutePrimitive(plan, pickPrimitive(plan, workspace, workspace_bytes), workspace,
+                                            workspace_bytes, stream);
     }
 
     // The clean-up calls below overwrite the thread's last result; the failing

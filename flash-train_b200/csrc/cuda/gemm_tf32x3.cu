@@ -38,6 +38,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "gemm_kernels.hpp"
 #include "ptx.cuh"
@@ -482,6 +483,18 @@ std::uint32_t chooseSplits(std::uint64_t tiles, std::uint64_t k, int sms) {
     return best;
 }
 
+// K blocks accumulated inside the tensor core between two drains. 8 blocks =
+// 256 K elements. FTCUDA_TF32_CHUNK_K_BLOCKS overrides it (a tuning knob for
+// accuracy/throughput experiments; read at Plan creation).
+std::uint32_t chunkKBlocks() {
+    const char* text = std::getenv("FTCUDA_TF32_CHUNK_K_BLOCKS");
+    if (text != nullptr) {
+        const long value = std::strtol(text, nullptr, 10);
+        if (value >= 1 && value <= (1L << 20)) { return static_cast<std::uint32_t>(value); }
+    }
+    return 8;
+}
+
 }  // namespace
 
 const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
@@ -521,7 +534,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     state.grid_z              = 1;
     state.block               = kThreads;
     state.smem_bytes          = kSmemBytes;
-    state.chunk_k_blocks      = 8;  // 256 K elements between drains
+    state.chunk_k_blocks      = chunkKBlocks();
     state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
     if (!encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
                            static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float), kTileK, kTileM, true, message,

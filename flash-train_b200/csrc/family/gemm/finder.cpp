@@ -11,12 +11,13 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 }  // namespace
 
 // Regime map on B200 (148 SMs; the count is queried, not assumed):
-//   * very few rows of A (m <= 16): B is streamed exactly once, the problem is
+//   * very few rows of A (m <= 32): B is streamed exactly once, the problem is
 //     HBM-bound -> the skinny kernel first.
 //   * enough rows/columns to fill 128x256 tensor-core tiles: 3xTF32 on tcgen05.
-//     If those tiles cover less than half of the SMs while K is long, the
-//     split-K variant (workspace needed) goes first so the idle SMs take
-//     K-slices; the unsplit kernels follow for callers without workspace.
+//     If the last wave of those tiles would leave more than a tenth of the SMs
+//     idle while K is long enough to cut, the split-K variant (workspace
+//     needed) goes first so that K slices even out the waves; the unsplit
+//     kernels follow for callers without workspace.
 //   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
 //     leave most SMs idle and K is long.
 // Every list ends with "Fp32Gemm", which needs no workspace and accepts every
@@ -35,12 +36,14 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     const char* simt_split   = cudaGemmName(FTCUDA_GEMM_SIMT_SPLITK);
 
     if (shape.m * shape.n == 0) { return {simt}; }
-    if (shape.m <= 16 && shape.k >= 256) { return {skinny, simt}; }
+    if (shape.m <= 32 && shape.k >= 256) { return {skinny, simt_split, simt}; }
 
     const bool fills_tensor_tiles = shape.m >= 128 && shape.n >= 128 && shape.k >= 256;
     if (fills_tensor_tiles) {
         const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 256);
-        if (tiles * 2 <= sm_count && shape.k >= 4096) { return {tensor_split, tensor, simt_split, simt}; }
+        const std::uint64_t waves = ceilDiv(tiles, sm_count);
+        const bool ragged         = tiles * 10 < waves * sm_count * 9;  // last wave under 90 % full overall
+        if (ragged && shape.k >= 8192) { return {tensor_split, tensor, simt_split, simt}; }
         return {tensor, simt};
     }
     const std::uint64_t simt_tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 128);

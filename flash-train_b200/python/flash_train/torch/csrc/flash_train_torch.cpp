@@ -1,13 +1,19 @@
 // flash_train.torch.gemm: D = alpha * (A @ B) + beta * C on torch's current
-// CUDA stream, through the one-shot C entry point ftrainGemm.
+// CUDA stream.
 //
 // Same Python signature and checks as the reference binding
 // (python/flash_train/torch/csrc/flash_train_torch.cpp:34-75 and
-// flash_train_torch_capi.cpp:11-33 there). Two things are done differently:
-// the current stream is asked of c10 directly instead of through a Python call
-// (the reference needs that detour because HIP and torch headers clash; the
-// public header of this build includes no GPU header), and a failure carries
-// the library's diagnostic message, not only the status number.
+// flash_train_torch_capi.cpp:11-33 there). Three things are done differently:
+//   * the current stream is asked of c10 directly instead of through a Python
+//     call (the reference needs that detour because HIP and torch headers
+//     clash; the public header of this build includes no GPU header);
+//   * the reference calls ftrainGemm with no workspace, which is enough for its
+//     one workspace-free kernel. Here the recommended Primitive can be a
+//     split-K kernel that needs one, so the binding makes the same staged calls
+//     ftrainGemm makes (Args, Plan, execute primitive 0) and, in between, asks
+//     the Plan how much workspace primitive 0 wants and takes it from torch's
+//     caching allocator;
+//   * a failure carries the library's diagnostic message, not only the status.
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -37,6 +43,35 @@ FTrainStorageView hostScalarView(const float* value) {
                              FTRAIN_INDEX_TYPE_CONTINUOUS, true};
 }
 
+// Pattern -> Ops for the Gemm graph, made once per process (what ftrainGemm
+// keeps internally, src/api/gemm_api.cpp:28-49 of the reference).
+struct GemmRoles {
+    FTrainOps ops{nullptr};
+    FTrainTensorId a{}, b{}, c{}, d{}, alpha{}, beta{};
+    FTrainGemmOpId gemm{};
+    FTrainStatus status{FTRAIN_STATUS_SUCCESS};
+};
+
+const GemmRoles& gemmRoles() {
+    static const GemmRoles roles = [] {
+        GemmRoles made;
+        FTrainPattern pattern         = nullptr;
+        FTrainStatus status           = ftrainPatternCreate(&pattern);
+        FTrainTensorId* const order[] = {&made.a, &made.b, &made.c, &made.alpha, &made.beta, &made.d};
+        for (FTrainTensorId* role : order) {
+            if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainPatternAddTensor(pattern, role); }
+        }
+        if (status == FTRAIN_STATUS_SUCCESS) {
+            status = ftrainPatternAddGemm(pattern, &made.gemm, made.a, made.b, made.c, made.d, made.alpha, made.beta);
+        }
+        if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainOpsCreate(&made.ops, pattern); }
+        if (pattern != nullptr) { ftrainPatternDestroy(pattern); }
+        made.status = status;
+        return made;
+    }();
+    return roles;
+}
+
 at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& c, double alpha,
                 double beta) {
     checkMatrix(a, "a");
@@ -60,13 +95,43 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const std::optional<at
     const float beta_value        = static_cast<float>(beta);
     const auto stream = reinterpret_cast<FTrainStream>(c10::cuda::getCurrentCUDAStream(a.device().index()).stream());
 
-    const FTrainStatus status =
-        ftrainGemm(matrixView(a.data_ptr(), a_dims), matrixView(b.data_ptr(), b_dims),
-                   matrixView(c.has_value() ? c->data_ptr() : nullptr, cd_dims), matrixView(d.data_ptr(), cd_dims),
-                   hostScalarView(&alpha_value), hostScalarView(&beta_value), FTRAIN_NUMERIC_TYPE_FP32, nullptr, 0,
-                   stream);
-    TORCH_CHECK(status == FTRAIN_STATUS_SUCCESS, "ftrainGemm failed with status ", static_cast<unsigned>(status), ": ",
-                ftrainGetLastMessage());
+    const GemmRoles& roles = gemmRoles();
+    TORCH_CHECK(roles.status == FTRAIN_STATUS_SUCCESS, "flash_train could not set up its Gemm Ops, status ",
+                static_cast<unsigned>(roles.status));
+    FTrainArgs args     = nullptr;
+    FTrainPlan plan     = nullptr;
+    FTrainStatus status = ftrainArgsCreate(&args, roles.ops);
+    const struct {
+        FTrainTensorId role;
+        FTrainStorageView view;
+    } bindings[] = {{roles.a, matrixView(a.data_ptr(), a_dims)},
+                    {roles.b, matrixView(b.data_ptr(), b_dims)},
+                    {roles.c, matrixView(c.has_value() ? c->data_ptr() : nullptr, cd_dims)},
+                    {roles.d, matrixView(d.data_ptr(), cd_dims)},
+                    {roles.alpha, hostScalarView(&alpha_value)},
+                    {roles.beta, hostScalarView(&beta_value)}};
+    for (const auto& binding : bindings) {
+        if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainArgsSetTensor(args, binding.role, binding.view); }
+    }
+    if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainArgsSetGemm(args, roles.gemm, FTRAIN_NUMERIC_TYPE_FP32); }
+    if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainPlanCreate(&plan, args); }
+    std::uint64_t workspace_bytes = 0;
+    if (status == FTRAIN_STATUS_SUCCESS) { status = ftrainPlanGetPrimitiveRequiredWorkspaceBytes(plan, 0, &workspace_bytes); }
+    at::Tensor workspace;
+    if (status == FTRAIN_STATUS_SUCCESS) {
+        if (workspace_bytes != 0) {
+            workspace = torch::empty({static_cast<std::int64_t>(workspace_bytes)}, a.options().dtype(at::kByte));
+        }
+        // The caching allocator keeps the block reserved for this stream until
+        // the enqueued work is done, so `workspace` may go out of scope below.
+        status = ftrainPlanExecutePrimitive(plan, 0, workspace_bytes != 0 ? workspace.data_ptr() : nullptr,
+                                            workspace_bytes, stream);
+    }
+    const std::string failure = status == FTRAIN_STATUS_SUCCESS ? std::string() : std::string(ftrainGetLastMessage());
+    if (plan != nullptr) { ftrainPlanDestroy(plan); }
+    if (args != nullptr) { ftrainArgsDestroy(args); }
+    TORCH_CHECK(status == FTRAIN_STATUS_SUCCESS, "flash_train gemm failed with status ", static_cast<unsigned>(status),
+                ": ", failure);
     return d;
 }
 

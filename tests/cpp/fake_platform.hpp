@@ -1,0 +1,39 @@
+// A fake of the platform layer's C ABI (ftcuda/ftcuda.h) for host-only tests:
+// a settable "current device", and configure/launch calls that are recorded
+// instead of touching a GPU. The host pipeline is linked against this fake in
+// the C++ test binary, the way the reference's engine tests inject mock
+// policies instead of faking a device (tests/engine/engine_test.cpp:59-201 there).
+#ifndef FTRAIN_TESTS_FAKE_PLATFORM_HPP_
+#define FTRAIN_TESTS_FAKE_PLATFORM_HPP_
+
+#include <cstdint>
+#include <vector>
+
+#include "ftcuda/ftcuda.h"
+
+namespace fake {
+
+struct LaunchRecord {
+    int kernel;
+    void* workspace;
+    std::uint64_t workspace_bytes;
+    void* stream;
+    FtcudaGemmDesc desc;
+};
+
+struct State {
+    int device               = 0;
+    bool device_query_fails  = false;
+    int sm_count             = 148;
+    std::uint64_t split_k_workspace = 4096;  // what the fake split-K kernels ask for
+    std::vector<LaunchRecord> launches;
+    int configures = 0;
+    int supports   = 0;
+};
+
+State& state();
+void reset();
+
+}  // namespace fake
+
+#endif

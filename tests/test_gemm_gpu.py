@@ -34,6 +34,10 @@ def gpu(capi):
 
 def platform_gemm(capi, gpu, kernel, a, b, c, alpha, beta, d=None):
     """Runs one kernel family through ftcuda_gemm_configure / ftcuda_gemm_launch."""
+    import os
+
+    if kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK) and os.environ.get("FT_SKIP_TENSOR"):
+        return None, "tensor-core kernels switched off by FT_SKIP_TENSOR"
     m, n = a.shape[0], b.shape[1]
     if d is None:
         d = torch.full((m, n), float("nan"), device="cuda")
@@ -277,6 +281,12 @@ def test_config3_tail_sweep_contiguous_and_transposed(capi, gpu, oracle, m):
         assert gpu.make_plan(a_view, b, None, d).primitive_names() == names
     if m <= 17:
         assert gpu.make_plan(a, b, None, d).primitive_name(0) == "Fp32GemmSkinny"
+    # The one-shot call takes no workspace here and must still succeed.
+    once = torch.empty(m, n, device="cuda")
+    capi.gemm_once(gpu.operand(a), gpu.operand(b), capi.null_operand(m, n), gpu.operand(once), 1.0, 0.0,
+                   stream=gpu.current_stream())
+    torch.cuda.synchronize()
+    check_against_float64(oracle, once, a, b, None, 1.0, 0.0, f"m={m} one-shot")
 
 
 def test_config4_training_shape_rows_sampled(capi, gpu, oracle):
