@@ -117,9 +117,9 @@ TEST(key_ignores_insertion_order) {
         const auto mapping = matchPatterns(shuffled, canonical);
         CHECK(mapping.has_value());
         if (mapping.has_value()) {
-            // User role added at position order[slot] plays canonical role `slot`... of the
-            // canonical builder, where roles were added in the order a,b,c,alpha,beta,d.
-            for (int slot = 0; slot < 6; ++slot) { CHECK_EQ(mapping->operand[order[slot]], static_cast<std::uint64_t>(slot)); }
+            // The operand added at position `slot` plays role order[slot] (a,b,c,alpha,beta,d = 0..5), and the
+            // canonical builder added its roles in exactly that order.
+            for (int slot = 0; slot < 6; ++slot) { CHECK_EQ(mapping->operand[slot], static_cast<std::uint64_t>(order[slot])); }
         }
     }
     CHECK(chained(false, false).getKey() == chained(false, true).getKey());
