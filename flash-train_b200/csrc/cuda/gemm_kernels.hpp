@@ -76,6 +76,9 @@ bool tmaEligible(const void* base, std::int64_t contiguous_stride, std::int64_t 
 const char* supportsSimt(const FtcudaGemmDesc& desc, bool split_k);
 int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t capacity);
 cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream);
+// Fills grid, block and K slicing of the predicated (any layout) SIMT kernel for
+// about `splits` K slices. Pure arithmetic on state.desc: no device call.
+void planSimtGenericSplitK(LaunchState& state, std::uint32_t splits);
 
 const char* supportsSkinny(const FtcudaGemmDesc& desc);
 int configureSkinny(LaunchState& state, char* message, std::size_t capacity);

@@ -428,6 +428,19 @@ int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t c
     return 0;
 }
 
+void planSimtGenericSplitK(LaunchState& state, std::uint32_t splits) {
+    const FtcudaGemmDesc& desc = state.desc;
+    state.variant              = kVariantGeneric;
+    state.grid_x               = static_cast<std::uint32_t>(ceilDiv(desc.n, kGenericTile));
+    state.grid_y               = static_cast<std::uint32_t>(ceilDiv(desc.m, kGenericTile));
+    state.block                = kThreads;
+    state.smem_bytes           = 0;
+    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, splits), kGenericK) * kGenericK);
+    state.splits      = static_cast<std::uint32_t>(ceilDiv(desc.k, state.k_per_split));
+    state.grid_z      = state.splits;
+    state.workspace_bytes = static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float);
+}
+
 cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream) {
     const SimtParams out = makeOutputParams(state, workspace);
     const dim3 grid(state.grid_x, state.grid_y, state.grid_z);

@@ -49,7 +49,7 @@ EXPORTED_SYMBOLS = (
 PLATFORM_SYMBOLS = (
     "ftcuda_current_device ftcuda_device_sm_count ftcuda_gemm_supports ftcuda_gemm_configure "
     "ftcuda_gemm_workspace_bytes ftcuda_gemm_launch ftcuda_launch_count ftcuda_trace_push ftcuda_trace_pop "
-    "ftcuda_trace_mark"
+    "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity"
 ).split()
 
 
@@ -406,8 +406,11 @@ def _declare_platform(lib) -> None:
     lib.ftcuda_gemm_workspace_bytes.argtypes = [POINTER(GemmLaunch)]
     lib.ftcuda_gemm_workspace_bytes.restype = c_uint64
     lib.ftcuda_gemm_launch.argtypes = [POINTER(GemmLaunch), c_void_p, c_uint64, c_void_p] + message
+    lib.ftcuda_gemm_splitk_static.argtypes = [POINTER(GemmDesc), c_void_p] + message
+    lib.ftcuda_gemm_splitk_static_capacity.argtypes = []
+    lib.ftcuda_gemm_splitk_static_capacity.restype = c_uint64
     for name in ("ftcuda_current_device", "ftcuda_device_sm_count", "ftcuda_gemm_supports", "ftcuda_gemm_configure",
-                 "ftcuda_gemm_launch"):
+                 "ftcuda_gemm_launch", "ftcuda_gemm_splitk_static"):
         getattr(lib, name).restype = ctypes.c_int
 
 
@@ -449,3 +452,14 @@ def platform_supports(kernel: int, desc: GemmDesc) -> str | None:
     if lib.ftcuda_gemm_supports(kernel, byref(desc), buffer, 256) != 0:
         return buffer.value.decode()
     return None
+
+
+def splitk_static(desc: GemmDesc, stream: int = 0) -> None:
+    """ftcuda_gemm_splitk_static: split-K GEMM on the library's own static scratch; allocates nothing."""
+    buffer = ctypes.create_string_buffer(256)
+    if lib.ftcuda_gemm_splitk_static(byref(desc), c_void_p(stream), buffer, 256) != 0:
+        raise FTrainError(STATUS_UNSUPPORTED, buffer.value.decode())
+
+
+def splitk_static_capacity() -> int:
+    return int(lib.ftcuda_gemm_splitk_static_capacity())

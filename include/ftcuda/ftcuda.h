@@ -99,6 +99,35 @@ FTCUDA_API uint64_t ftcuda_gemm_workspace_bytes(const FtcudaGemmLaunch* launch);
 FTCUDA_API int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
                                   void* stream, char* message, size_t message_capacity);
 
+/*
+ * Exact-FP32 split-K GEMM that needs no workspace from the caller and allocates
+ * nothing. It has no counterpart in the reference, whose only kernel needs no
+ * scratch memory at all.
+ *
+ * It exists for callers that cannot supply or allocate a workspace: code
+ * running after a framework has taken all device memory into its own pool,
+ * latency-critical loops that must avoid the device-wide synchronisation
+ * inside cudaMalloc/cudaFree, and bindings that always pass a null workspace.
+ * The partial sums of the K slices live in a 16 MiB array inside the library
+ * image (one copy on every GPU that loads the library, kept until exit;
+ * ftcuda_gemm_splitk_static_capacity returns its size in bytes).
+ *
+ *   - desc->device must be the calling thread's current device.
+ *   - slices * m * n * 4 bytes must fit the array with at least two slices,
+ *     i.e. m * n <= 2 Mi elements; larger outputs are refused with a message.
+ *   - The first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside of stream capture.
+ *   - All calls on a GPU share the array. Nothing in it has to be cleared
+ *     between calls (every element read is written first in the same call),
+ *     but calls that can overlap on the GPU race on it: serialise them, for
+ *     instance on one stream.
+ * Same arithmetic as FTCUDA_GEMM_SIMT_SPLITK: FP32 FFMA per slice, slices summed
+ * in order. Returns 0, or nonzero with a reason in `message`.
+ */
+FTCUDA_API int ftcuda_gemm_splitk_static(const FtcudaGemmDesc* desc, void* stream, char* message,
+                                         size_t message_capacity);
+FTCUDA_API uint64_t ftcuda_gemm_splitk_static_capacity(void);
+
 /* Number of device kernels ftcuda_gemm_launch has enqueued from this process;
  * benchmarks read it to report how many launches a timed region made. */
 FTCUDA_API uint64_t ftcuda_launch_count(void);
