@@ -4,32 +4,38 @@
 // three tcgen05.mma.kind::tf32 products accumulated in FP32 in tensor memory.
 // The dropped a_lo*b_lo term is below 2^-22 of |a*b|.
 //
-// One CTA per SM, persistent over 128 x 256 output tiles, K walked in blocks
-// of 32. Sixteen warps in four roles, connected only by mbarriers:
+// One CTA per SM, persistent over 128 x 192 output tiles, K walked in blocks
+// of 32. Sixteen warps in five roles, connected only by mbarriers:
 //
-//   warp 0      TMA producer. Per K block it fetches the 128x32 A tile straight
-//               into the stage's A_hi buffer (128-byte swizzle: already the
-//               K-major layout the MMA wants) and the 32x256 B tile as eight
-//               32(k) x 32(n) swizzled boxes into a small raw ring.
-//   warps 4-7   converters. They split A in place (A_hi overwritten with the
-//               TF32-rounded value, A_lo next to it) and transpose-and-split
-//               the raw B boxes into K-major B_hi / B_lo tiles, so both MMA
-//               operands are K-major with the 128-byte swizzle. Reads and
-//               writes are arranged to be bank-conflict free (lane <-> k).
-//   warp 1      MMA issuer (one thread): 4 K-steps x 3 products per K block
-//               into the "chunk" accumulator (TMEM columns 0-255); a
-//               tcgen05.commit per K block hands the stage back to the producer.
+//   warp 0      TMA producer. Per K block it fetches the raw FP32 operands into
+//               one slot of a 3-deep ring: the 128x32 A tile (rows of 128 bytes,
+//               128-byte swizzle) and the 32x192 B tile as six 32(k) x 32(n)
+//               swizzled boxes. Three K blocks of raw data in flight cover the
+//               L2 latency, independently of the stages below.
+//   warps 4-7   A converters, one thread per row of A: they read their row from
+//               the raw slot, split it and store a_hi / a_lo into TENSOR MEMORY
+//               (tcgen05.st), from where the MMA takes its A operand. A never
+//               occupies MMA-side shared memory or its read bandwidth.
+//   warps 2-7   B converters, one 32x32 box per warp: transpose-and-split into
+//               K-major B_hi / B_lo shared-memory tiles (128-byte swizzle), the
+//               layout of the B operand of a "TN" GEMM. Lane <-> k makes both
+//               the 128-bit reads and the 32-bit writes bank-conflict free.
+//   warp 1      MMA issuer (one thread): 4 K-steps x 3 products per K block,
+//               A from tensor memory, B by shared-memory descriptor, into the
+//               "chunk" accumulator (TMEM columns 0-191). A tcgen05.commit per
+//               K block releases the stage (its B tiles and its A columns).
 //   warps 8-15  drain / epilogue. Every `chunk_k_blocks` K blocks the chunk
 //               accumulator is added, in round-to-nearest FP32, to a running
-//               sum kept in TMEM columns 256-511, and the chunk restarts from
-//               zero (default: every 4 K blocks). This bounds the length of any accumulation chain inside
-//               the tensor core, whose internal FP32 additions are not
-//               round-to-nearest. After the last chunk the sum is scaled and
-//               written out (or stored raw as a split-K partial) while the
-//               next tile's first chunk is already being multiplied.
+//               sum kept in TMEM columns 192-383, and the chunk restarts from
+//               zero (default: every 4 K blocks). This bounds the length of any
+//               accumulation chain inside the tensor core, whose internal FP32
+//               additions truncate. After the last chunk the sum is scaled and
+//               written out (or stored raw as a split-K partial) while the next
+//               tile's first chunk is already being multiplied.
 //
-// Shared memory: 2 stages x (A_hi 16 + A_lo 16 + B_hi 32 + B_lo 32 KiB) plus a
-// 2 x 16 KiB raw-B ring = 224 KiB. Tensor memory: all 512 columns.
+// Shared memory: 3 raw slots x 40 KiB + 2 stages x (B_hi 24 + B_lo 24 KiB) =
+// 216 KiB. Tensor memory: chunk 192 + running 192 + 2 stages x (A_hi 32 +
+// A_lo 32) columns = 512.
 //
 // Every wait is bounded (ptx.cuh). A wait that gives up raises the CTA's abort
 // flag; all roles then stop, outstanding copies and MMAs are given time to
@@ -47,27 +53,35 @@ namespace ftcuda {
 namespace {
 
 constexpr int kTileM  = 128;
-constexpr int kTileN  = 256;
+constexpr int kTileN  = 192;
 constexpr int kTileK  = 32;
-constexpr int kStages = 2;
+constexpr int kStages   = 2;  // converted (hi/lo) stages
+constexpr int kRawSlots = 3;  // raw K blocks in flight
 
-constexpr int kAHiOffset    = 0;
-constexpr int kALoOffset    = 16384;
-constexpr int kBHiOffset    = 32768;
-constexpr int kBLoOffset    = 65536;
-constexpr int kStageBytes   = 98304;
-constexpr int kRawSlotBytes = 16384;  // 32 k x 128 n, as four 4 KiB boxes
-constexpr int kRawOffset    = kStages * kStageBytes;
-constexpr int kBarrierOffset = kRawOffset + 2 * kRawSlotBytes;
+constexpr int kRawABytes    = kTileM * kTileK * 4;        // 16 KiB
+constexpr int kBoxBytes     = 32 * 32 * 4;                // one 32(k) x 32(n) box of B
+constexpr int kBoxes        = kTileN / 32;                // 6
+constexpr int kRawSlotBytes = kRawABytes + kBoxes * kBoxBytes;  // 40 KiB
+constexpr int kBTileBytes   = kTileN * kTileK * 4;        // 24 KiB, K-major
+constexpr int kBHiOffset    = 0;
+constexpr int kBLoOffset    = kBTileBytes;
+constexpr int kStageBytes   = 2 * kBTileBytes;
+constexpr int kStageOffset  = kRawSlots * kRawSlotBytes;
+constexpr int kBarrierOffset = kStageOffset + kStages * kStageBytes;
 constexpr int kSmemBytes     = kBarrierOffset + 256 + 1024;  // + barriers + alignment slack
 
-constexpr int kThreads        = 512;
-constexpr int kProducerWarp   = 0;
-constexpr int kMmaWarp        = 1;
-constexpr int kFirstConverter = 4;   // warps 4..7
-constexpr int kFirstEpilogue  = 8;   // warps 8..15
-constexpr int kTmemColumns    = 512;
-constexpr int kRunningColumn  = 256;
+constexpr int kThreads         = 512;
+constexpr int kProducerWarp    = 0;
+constexpr int kMmaWarp         = 1;
+constexpr int kFirstConverter  = 2;  // warps 2..7 convert B; warps 4..7 also convert A
+constexpr int kFirstAConverter = 4;
+constexpr int kConverterWarps  = 6;
+constexpr int kFirstEpilogue   = 8;  // warps 8..15
+constexpr int kTmemColumns     = 512;
+constexpr int kRunningColumn   = kTileN;       // running sum: columns 192..383
+constexpr int kAColumn         = 2 * kTileN;   // A operands: 64 columns per stage from 384
+constexpr int kHalfColumns     = kTileN / 2;   // columns per epilogue warp
+constexpr int kPieces          = kHalfColumns / 16;
 
 // Rows of M tiles walked together so that concurrently running CTAs share B
 // panels in L2.
@@ -88,11 +102,10 @@ struct TensorParams {
 };
 
 struct Barriers {
-    std::uint64_t a_full[kStages];
+    std::uint64_t raw_full[kRawSlots];
+    std::uint64_t raw_empty[kRawSlots];
     std::uint64_t mma_done[kStages];
     std::uint64_t conv_done[kStages];
-    std::uint64_t raw_full[2];
-    std::uint64_t raw_empty[2];
     std::uint64_t acc_full;
     std::uint64_t acc_empty;
     std::uint64_t flush;
@@ -200,14 +213,13 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbarrierInit(&bars->a_full[s], 1);
-            mbarrierInit(&bars->mma_done[s], 1);
-            mbarrierInit(&bars->conv_done[s], 4);
+        for (int r = 0; r < kRawSlots; ++r) {
+            mbarrierInit(&bars->raw_full[r], 1);
+            mbarrierInit(&bars->raw_empty[r], kConverterWarps);
         }
-        for (int h = 0; h < 2; ++h) {
-            mbarrierInit(&bars->raw_full[h], 1);
-            mbarrierInit(&bars->raw_empty[h], 4);
+        for (int s = 0; s < kStages; ++s) {
+            mbarrierInit(&bars->mma_done[s], 1);
+            mbarrierInit(&bars->conv_done[s], kConverterWarps);
         }
         mbarrierInit(&bars->acc_full, 1);
         mbarrierInit(&bars->acc_empty, 8);
@@ -223,39 +235,33 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tcgen05FenceAfterSync();
     const std::uint32_t tmem_base = bars->tmem_base;
 
-    // The producer and MMA warps walk their loops with all 32 lanes (so the
-    // warp stays converged for the block-wide barrier at the end); lane 0 alone
-    // issues copies, MMAs and commits.
+    // Every role walks the same list of work items and K blocks; `it` counts K
+    // blocks over all items and selects the raw slot (it % 3) and the stage
+    // (it % 2). The producer and MMA warps keep all 32 lanes in their loops (so
+    // that the warp is converged at the block-wide barrier at the end); lane 0
+    // alone issues copies, MMAs and commits.
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ producer
-        std::uint32_t it = 0;  // K blocks issued so far, over all items
+        std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             const WorkItem w = decodeItem(p, item);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const std::uint32_t s      = it % kStages;
-                const std::uint32_t use    = it / kStages;
-                unsigned char* stage       = smem + s * kStageBytes;
+                const std::uint32_t r      = it % kRawSlots;
+                const std::uint32_t use    = it / kRawSlots;
+                unsigned char* slot        = smem + r * kRawSlotBytes;
                 const std::int32_t k_coord = static_cast<std::int32_t>(w.k_begin + kb * kTileK);
-                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->mma_done[s], (use & 1) ^ 1, abort_flag));
+                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->raw_empty[r], (use & 1) ^ 1, abort_flag));
                 if (!ok) { break; }
                 if (lane == 0) {
-                    mbarrierArriveExpectTx(&bars->a_full[s], kTileM * kTileK * 4);
-                    tmaLoad2d(stage + kAHiOffset, &map_a, &bars->a_full[s], k_coord, static_cast<std::int32_t>(w.tile_m));
-                }
-                for (int h = 0; h < 2 && ok; ++h) {
-                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->raw_empty[h], (it & 1) ^ 1, abort_flag));
-                    if (!ok) { break; }
-                    if (lane == 0) {
-                        unsigned char* slot = smem + kRawOffset + h * kRawSlotBytes;
-                        mbarrierArriveExpectTx(&bars->raw_full[h], kRawSlotBytes);
-                        for (int q = 0; q < 4; ++q) {
-                            tmaLoad2d(slot + q * 4096, &map_b, &bars->raw_full[h],
-                                      static_cast<std::int32_t>(w.tile_n + h * 128 + q * 32), k_coord);
-                        }
+                    mbarrierArriveExpectTx(&bars->raw_full[r], kRawSlotBytes);
+                    tmaLoad2d(slot, &map_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
+                    for (int q = 0; q < kBoxes; ++q) {
+                        tmaLoad2d(slot + kRawABytes + q * kBoxBytes, &map_b, &bars->raw_full[r],
+                                  static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
                     }
-                    __syncwarp();
                 }
+                __syncwarp();
             }
         }
         if (!ok) { *abort_flag = 1; }
@@ -281,20 +287,20 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) { break; }
                 tcgen05FenceAfterSync();
                 if (lane == 0) {
-                    const std::uint32_t stage = smemAddress(smem + s * kStageBytes);
-                    const std::uint64_t a_hi  = umaDescriptorK128(stage + kAHiOffset);
-                    const std::uint64_t a_lo  = umaDescriptorK128(stage + kALoOffset);
+                    const std::uint32_t stage = smemAddress(smem + kStageOffset + s * kStageBytes);
                     const std::uint64_t b_hi  = umaDescriptorK128(stage + kBHiOffset);
                     const std::uint64_t b_lo  = umaDescriptorK128(stage + kBLoOffset);
+                    const std::uint32_t a_hi  = tmem_base + kAColumn + s * 64;
+                    const std::uint32_t a_lo  = a_hi + 32;
 #pragma unroll
                     for (int step = 0; step < kTileK / 8; ++step) {
-                        // 8 TF32 elements = 32 bytes further along K: +2 in
-                        // the descriptor's 16-byte address units.
+                        // 8 TF32 elements further along K: 8 columns of tensor
+                        // memory for A, 32 bytes = +2 descriptor units for B.
                         const std::uint64_t advance = static_cast<std::uint64_t>(step * 2);
                         const std::uint32_t fresh   = (chunk_start && step == 0) ? 0U : 1U;
-                        umaTf32(tmem_base, a_lo + advance, b_hi + advance, kInstruction, fresh);
-                        umaTf32(tmem_base, a_hi + advance, b_lo + advance, kInstruction, 1U);
-                        umaTf32(tmem_base, a_hi + advance, b_hi + advance, kInstruction, 1U);
+                        umaTf32TmemA(tmem_base, a_lo + step * 8, b_hi + advance, kInstruction, fresh);
+                        umaTf32TmemA(tmem_base, a_hi + step * 8, b_lo + advance, kInstruction, 1U);
+                        umaTf32TmemA(tmem_base, a_hi + step * 8, b_hi + advance, kInstruction, 1U);
                     }
                     umaCommit(&bars->mma_done[s]);
                     const bool chunk_end = (kb + 1) % p.chunk_k_blocks == 0 || kb + 1 == w.k_blocks;
@@ -315,63 +321,79 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp >= kFirstConverter && warp < kFirstEpilogue) {
         // ------------------------------------------------------------ converters
-        const int cw        = warp - kFirstConverter;            // 0..3, also the B box this warp owns
-        const int t         = threadIdx.x - kFirstConverter * 32;  // 0..127
-        std::uint32_t it    = 0;
-        bool ok             = true;
+        const int box_index   = warp - kFirstConverter;  // the B box this warp owns, 0..5
+        const bool converts_a = warp >= kFirstAConverter;
+        const int a_row       = 32 * (warp & 3) + lane;   // row of A = TMEM lane (warp % 4 selects the lane quadrant)
+        // Lanes 16-31 take their k rows of a B box in an order shifted by four.
+        const int kk = lane ^ ((lane & 16) >> 2);
+        std::uint32_t it = 0;
+        bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
             const WorkItem w = decodeItem(p, item);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const std::uint32_t s   = it % kStages;
-                const std::uint32_t use = it / kStages;
-                unsigned char* stage    = smem + s * kStageBytes;
-                ok = mbarrierWait(&bars->a_full[s], use & 1, abort_flag);
+                const std::uint32_t r      = it % kRawSlots;
+                const std::uint32_t s      = it % kStages;
+                const unsigned char* slot  = smem + r * kRawSlotBytes;
+                unsigned char* stage       = smem + kStageOffset + s * kStageBytes;
+                ok = mbarrierWait(&bars->raw_full[r], (it / kRawSlots) & 1, abort_flag);
                 if (!ok) { break; }
-                // A: elementwise, in place for the high part.
+                // The stage (B tiles and A columns) is free once the MMAs of its
+                // previous use have completed.
+                ok = mbarrierWait(&bars->mma_done[s], ((it / kStages) & 1) ^ 1, abort_flag);
+                if (!ok) { break; }
+                tcgen05FenceAfterSync();
+                if (converts_a) {
+                    // One row of A per thread: 8 chunks of 4 floats, un-swizzled by
+                    // the row index, split, and stored to this stage's A columns.
+                    const unsigned char* row   = slot + a_row * 128;
+                    const std::uint32_t a_tmem = tmem_base + (static_cast<std::uint32_t>(32 * (warp & 3)) << 16) +
+                                                 kAColumn + s * 64;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int offset = (t + 128 * e) * 16;
-                    const float4 raw = *reinterpret_cast<const float4*>(stage + kAHiOffset + offset);
-                    uint4 hi, lo;
-                    splitTf32(raw.x, hi.x, lo.x);
-                    splitTf32(raw.y, hi.y, lo.y);
-                    splitTf32(raw.z, hi.z, lo.z);
-                    splitTf32(raw.w, hi.w, lo.w);
-                    *reinterpret_cast<uint4*>(stage + kAHiOffset + offset) = hi;
-                    *reinterpret_cast<uint4*>(stage + kALoOffset + offset) = lo;
+                    for (int half = 0; half < 2; ++half) {
+                        float hi[16];
+                        float lo[16];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int chunk  = half * 4 + c;
+                            const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
+                            const float values[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                std::uint32_t hi_bits, lo_bits;
+                                splitTf32(values[j], hi_bits, lo_bits);
+                                hi[c * 4 + j] = __uint_as_float(hi_bits);
+                                lo[c * 4 + j] = __uint_as_float(lo_bits);
+                            }
+                        }
+                        tmemStore16(a_tmem + half * 16, hi);
+                        tmemStore16(a_tmem + 32 + half * 16, lo);
+                    }
                 }
                 // B: one lane per k. A 128-bit read takes 4 consecutive n at one k
                 // from the raw box (rows of 128 bytes indexed by k, 16-byte chunks
                 // XOR-swizzled by k % 8); four 32-bit writes put them into rows n
                 // of the K-major tile (16-byte chunks XOR-swizzled by n % 8).
-                // Lanes 16-31 take their k rows in an order shifted by four, so
-                // that lanes l and l+16 never read the same bank group in one
-                // instruction, whichever eight lanes the hardware serves together.
-                const int kk = lane ^ ((lane & 16) >> 2);
-                for (int h = 0; h < 2 && ok; ++h) {
-                    ok = mbarrierWait(&bars->raw_full[h], it & 1, abort_flag);
-                    if (!ok) { break; }
-                    const unsigned char* box = smem + kRawOffset + h * kRawSlotBytes + cw * 4096;
+                const unsigned char* box = slot + kRawABytes + box_index * kBoxBytes;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const float4 raw = *reinterpret_cast<const float4*>(box + kk * 128 + ((c ^ (kk & 7)) << 4));
-                        const float values[4] = {raw.x, raw.y, raw.z, raw.w};
+                for (int c = 0; c < 8; ++c) {
+                    const float4 raw = *reinterpret_cast<const float4*>(box + kk * 128 + ((c ^ (kk & 7)) << 4));
+                    const float values[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int n_row = h * 128 + cw * 32 + c * 4 + j;
-                            const int dst   = n_row * 128 + (((kk >> 2) ^ (n_row & 7)) << 4) + (kk & 3) * 4;
-                            std::uint32_t hi, lo;
-                            splitTf32(values[j], hi, lo);
-                            *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
-                            *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        const int n_row = box_index * 32 + c * 4 + j;
+                        const int dst   = n_row * 128 + (((kk >> 2) ^ (n_row & 7)) << 4) + (kk & 3) * 4;
+                        std::uint32_t hi, lo;
+                        splitTf32(values[j], hi, lo);
+                        *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
+                        *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
                     }
-                    __syncwarp();
-                    if (lane == 0) { mbarrierArrive(&bars->raw_empty[h]); }
                 }
-                if (!ok) { break; }
-                // Publish the stage to the tensor core (async proxy).
+                __syncwarp();
+                if (lane == 0) { mbarrierArrive(&bars->raw_empty[r]); }
+                // Publish: shared-memory writes to the async proxy, tensor-memory
+                // stores (already waited for) to the MMA issuer.
                 fenceProxyAsync();
+                tcgen05FenceBeforeSync();
                 __syncwarp();
                 if (lane == 0) { mbarrierArrive(&bars->conv_done[s]); }
             }
@@ -381,7 +403,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------------------------------------ drain / epilogue
         const int e                   = warp - kFirstEpilogue;  // 0..7
         const std::uint32_t lane_base = static_cast<std::uint32_t>(32 * (e & 3));
-        const std::uint32_t col_half  = static_cast<std::uint32_t>(128 * (e >> 2));
+        const std::uint32_t col_half  = static_cast<std::uint32_t>(kHalfColumns * (e >> 2));
         const std::uint32_t tmem_row  = tmem_base + (lane_base << 16);
         std::uint32_t chunks          = 0;
         bool ok                       = true;
@@ -402,43 +424,30 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tcgen05FenceAfterSync();
                 const bool first = chunk == 0;
                 const bool last  = chunk + 1 == num_chunks;
-                if (last) {
-                    // Piece by piece: fold in the running sum and write out. The
-                    // chunk accumulator is released as soon as its last piece
-                    // has been read, before that piece is written.
+                // Piece by piece (16 columns): fold in the running sum, then
+                // either write the result out (last chunk) or store the new
+                // running sum. The chunk accumulator is released as soon as
+                // its last piece has been read.
 #pragma unroll
-                    for (int piece = 0; piece < 8; ++piece) {
-                        float sum[16];
-                        tmemLoad16(tmem_row + col_half + piece * 16, sum);
-                        if (!first) {
-                            float running[16];
-                            tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
+                for (int piece = 0; piece < kPieces; ++piece) {
+                    float sum[16];
+                    tmemLoad16(tmem_row + col_half + piece * 16, sum);
+                    if (!first) {
+                        float running[16];
+                        tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
-                        }
-                        if (piece == 7) {
-                            tcgen05FenceBeforeSync();
-                            __syncwarp();
-                            if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
-                        }
-                        writeRowSegment(p, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
+                        for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
                     }
-                } else {
-#pragma unroll
-                    for (int piece = 0; piece < 8; ++piece) {
-                        float sum[16];
-                        tmemLoad16(tmem_row + col_half + piece * 16, sum);
-                        if (!first) {
-                            float running[16];
-                            tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
-                        }
+                    if (piece == kPieces - 1) {
+                        tcgen05FenceBeforeSync();
+                        __syncwarp();
+                        if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
+                    }
+                    if (last) {
+                        writeRowSegment(p, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
+                    } else {
                         tmemStore16(tmem_row + kRunningColumn + col_half + piece * 16, sum);
                     }
-                    tcgen05FenceBeforeSync();
-                    __syncwarp();
-                    if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
                 }
             }
         }
@@ -451,13 +460,9 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (p.status != nullptr) { *p.status = 2; }
             // Copies that were armed but never consumed may still be landing.
             int never = 0;
-            for (int s = 0; s < kStages; ++s) {
-                mbarrierWait(&bars->a_full[s], 0, &never);
-                mbarrierWait(&bars->a_full[s], 1, &never);
-            }
-            for (int h = 0; h < 2; ++h) {
-                mbarrierWait(&bars->raw_full[h], 0, &never);
-                mbarrierWait(&bars->raw_full[h], 1, &never);
+            for (int r = 0; r < kRawSlots; ++r) {
+                mbarrierWait(&bars->raw_full[r], 0, &never);
+                mbarrierWait(&bars->raw_full[r], 1, &never);
             }
         }
         __syncthreads();

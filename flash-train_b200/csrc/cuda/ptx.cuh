@@ -162,6 +162,20 @@ __device__ __forceinline__ void umaTf32(std::uint32_t d_tmem, std::uint64_t a_de
         : "memory");
 }
 
+// Same with the A operand in tensor memory: M rows in lanes 0..M-1, the 8 K
+// elements of this instruction in 8 consecutive 32-bit columns at a_tmem.
+__device__ __forceinline__ void umaTf32TmemA(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_descriptor,
+                                             std::uint32_t instruction, std::uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_descriptor), "r"(instruction), "r"(accumulate)
+        : "memory");
+}
+
 // Arrives once on `barrier` when every MMA this thread issued so far has
 // finished (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umaCommit(std::uint64_t* barrier) {

@@ -13,7 +13,7 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 // Regime map on B200 (148 SMs; the count is queried, not assumed):
 //   * very few rows of A (m <= 32): B is streamed exactly once, the problem is
 //     HBM-bound -> the skinny kernel first.
-//   * enough rows/columns to fill 128x256 tensor-core tiles: 3xTF32 on tcgen05.
+//   * enough rows/columns to fill 128x192 tensor-core tiles: 3xTF32 on tcgen05.
 //     If the last wave of those tiles would leave more than a tenth of the SMs
 //     idle while K is long enough to cut, the split-K variant (workspace
 //     needed) goes first so that K slices even out the waves; the unsplit
@@ -40,7 +40,7 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
 
     const bool fills_tensor_tiles = shape.m >= 128 && shape.n >= 128 && shape.k >= 256;
     if (fills_tensor_tiles) {
-        const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 256);
+        const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 192);
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
         const bool ragged         = tiles * 10 < waves * sm_count * 9;  // last wave under 90 % full overall
         if (ragged && shape.k >= 8192) { return {tensor_split, tensor, simt_split, simt}; }
