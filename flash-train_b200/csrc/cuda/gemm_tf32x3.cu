@@ -5,7 +5,7 @@
 // The dropped a_lo*b_lo term is below 2^-22 of |a*b|.
 //
 // One CTA per SM, persistent over 128 x 192 output tiles, K walked in blocks
-// of 32. Sixteen warps in five roles, connected only by mbarriers:
+// of 32. Twenty warps in five roles, connected only by mbarriers:
 //
 //   warp 0      TMA producer. Per K block it fetches the raw FP32 operands into
 //               one slot of a 3-deep ring: the 128x32 A tile (rows of 128 bytes,
@@ -16,7 +16,8 @@
 //               the raw slot, split it and store a_hi / a_lo into TENSOR MEMORY
 //               (tcgen05.st), from where the MMA takes its A operand. A never
 //               occupies MMA-side shared memory or its read bandwidth.
-//   warps 2-7   B converters, one 32x32 box per warp: transpose-and-split into
+//   warps 2,3,  B converters, one 32x32 box per warp: transpose-and-split into
+//   16-19
 //               K-major B_hi / B_lo shared-memory tiles (128-byte swizzle), the
 //               layout of the B operand of a "TN" GEMM. Lane <-> k makes both
 //               the 128-bit reads and the 32-bit writes bank-conflict free.
@@ -70,13 +71,13 @@ constexpr int kStageOffset  = kRawSlots * kRawSlotBytes;
 constexpr int kBarrierOffset = kStageOffset + kStages * kStageBytes;
 constexpr int kSmemBytes     = kBarrierOffset + 256 + 1024;  // + barriers + alignment slack
 
-constexpr int kThreads         = 512;
+constexpr int kThreads         = 640;  // 20 warps
 constexpr int kProducerWarp    = 0;
 constexpr int kMmaWarp         = 1;
-constexpr int kFirstConverter  = 2;  // warps 2..7 convert B; warps 4..7 also convert A
-constexpr int kFirstAConverter = 4;
-constexpr int kConverterWarps  = 6;
-constexpr int kFirstEpilogue   = 8;  // warps 8..15
+constexpr int kFirstAConverter = 4;   // warps 4..7 convert A (warp % 4 = tensor-memory lane quadrant)
+constexpr int kFirstEpilogue   = 8;   // warps 8..15
+constexpr int kFirstLateB      = 16;  // warps 2, 3 and 16..19 convert B, one box each
+constexpr int kConverterWarps  = 4 + kBoxes;
 constexpr int kTmemColumns     = 512;
 constexpr int kRunningColumn   = kTileN;       // running sum: columns 192..383
 constexpr int kAColumn         = 2 * kTileN;   // A operands: 64 columns per stage from 384
@@ -319,10 +320,10 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             __syncwarp();
         }
-    } else if (warp >= kFirstConverter && warp < kFirstEpilogue) {
+    } else if (warp < kFirstEpilogue || warp >= kFirstLateB) {
         // ------------------------------------------------------------ converters
-        const int box_index   = warp - kFirstConverter;  // the B box this warp owns, 0..5
-        const bool converts_a = warp >= kFirstAConverter;
+        const bool converts_a = warp >= kFirstAConverter && warp < kFirstEpilogue;
+        const int box_index   = warp < kFirstAConverter ? warp - 2 : warp - kFirstLateB + 2;  // B box of a B converter
         const int a_row       = 32 * (warp & 3) + lane;   // row of A = TMEM lane (warp % 4 selects the lane quadrant)
         // Lanes 16-31 take their k rows of a B box in an order shifted by four.
         const int kk = lane ^ ((lane & 16) >> 2);
@@ -365,27 +366,30 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 lo[c * 4 + j] = __uint_as_float(lo_bits);
                             }
                         }
-                        tmemStore16(a_tmem + half * 16, hi);
-                        tmemStore16(a_tmem + 32 + half * 16, lo);
+                        tmemStore16NoWait(a_tmem + half * 16, hi);
+                        tmemStore16NoWait(a_tmem + 32 + half * 16, lo);
                     }
-                }
-                // B: one lane per k. A 128-bit read takes 4 consecutive n at one k
-                // from the raw box (rows of 128 bytes indexed by k, 16-byte chunks
-                // XOR-swizzled by k % 8); four 32-bit writes put them into rows n
-                // of the K-major tile (16-byte chunks XOR-swizzled by n % 8).
-                const unsigned char* box = slot + kRawABytes + box_index * kBoxBytes;
+                    tmemStoreWait();
+                } else {
+                    // B: one lane per k. A 128-bit read takes 4 consecutive n at one
+                    // k from the raw box (rows of 128 bytes indexed by k, 16-byte
+                    // chunks XOR-swizzled by k % 8); four 32-bit writes put them
+                    // into rows n of the K-major tile (16-byte chunks XOR-swizzled
+                    // by n % 8).
+                    const unsigned char* box = slot + kRawABytes + box_index * kBoxBytes;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float4 raw = *reinterpret_cast<const float4*>(box + kk * 128 + ((c ^ (kk & 7)) << 4));
-                    const float values[4] = {raw.x, raw.y, raw.z, raw.w};
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 raw = *reinterpret_cast<const float4*>(box + kk * 128 + ((c ^ (kk & 7)) << 4));
+                        const float values[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int n_row = box_index * 32 + c * 4 + j;
-                        const int dst   = n_row * 128 + (((kk >> 2) ^ (n_row & 7)) << 4) + (kk & 3) * 4;
-                        std::uint32_t hi, lo;
-                        splitTf32(values[j], hi, lo);
-                        *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
-                        *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
+                        for (int j = 0; j < 4; ++j) {
+                            const int n_row = box_index * 32 + c * 4 + j;
+                            const int dst   = n_row * 128 + (((kk >> 2) ^ (n_row & 7)) << 4) + (kk & 3) * 4;
+                            std::uint32_t hi, lo;
+                            splitTf32(values[j], hi, lo);
+                            *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
+                            *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
+                        }
                     }
                 }
                 __syncwarp();

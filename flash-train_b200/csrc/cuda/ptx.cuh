@@ -235,6 +235,23 @@ __device__ __forceinline__ void tmemStore16(std::uint32_t address, const float (
         : "memory");
 }
 
+// The same store without waiting for it; tmemStoreWait() completes all of a
+// thread's earlier tensor-memory stores.
+__device__ __forceinline__ void tmemStore16NoWait(std::uint32_t address, const float (&in)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(address),
+        "r"(__float_as_uint(in[0])), "r"(__float_as_uint(in[1])), "r"(__float_as_uint(in[2])),
+        "r"(__float_as_uint(in[3])), "r"(__float_as_uint(in[4])), "r"(__float_as_uint(in[5])),
+        "r"(__float_as_uint(in[6])), "r"(__float_as_uint(in[7])), "r"(__float_as_uint(in[8])),
+        "r"(__float_as_uint(in[9])), "r"(__float_as_uint(in[10])), "r"(__float_as_uint(in[11])),
+        "r"(__float_as_uint(in[12])), "r"(__float_as_uint(in[13])), "r"(__float_as_uint(in[14])),
+        "r"(__float_as_uint(in[15]))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmemStoreWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 }  // namespace ftcuda
 
 #endif
