@@ -2,15 +2,25 @@
 // where the whole cost is reading B once. HBM-bound; algorithmic traffic
 // 4 * (k * n + m * k + m * n [+ m * n]) bytes, of which k * n dominates.
 //
-// Each CTA owns a strip of 32 columns of B and walks all of K. A warp-wide
-// 128-bit load covers 4 rows of B x 32 columns (lane = row-in-group * 8 +
-// column-quad), so every request is four full 128-byte lines; eight such loads
-// are kept in flight per warp. The values of A are broadcast loads that hit
-// L1. The eight warps of a CTA take interleaved K rows; their partial sums
-// meet in a fixed order (shuffles across the 4 row groups of a warp, then
-// shared memory across warps), so results are deterministic. Sums are FP32
-// FFMA; the order over K differs from a sequential loop only by that fixed
-// partition.
+// Work split. A strip of 128 columns of B belongs to one thread-block CLUSTER
+// of up to 8 CTAs; the CTAs of a cluster take consecutive ranges of K, and the
+// eight warps of a CTA take interleaved groups of four K rows inside the range.
+// One warp instruction loads one K row of the strip: 32 lanes x 128 bits = 512
+// contiguous bytes, and a warp keeps two groups (eight such loads) in flight.
+// The four values A[i][k..k+3] a group needs for row i are one 128-bit load
+// whose address is the same for the whole warp (a broadcast that hits L1), so
+// the load/store unit sees about five instructions per four rows of B instead
+// of one per row and row of A.
+//
+// Reduction, all in a fixed order (results are deterministic): the warps of a
+// CTA add their partial sums one after the other into a shared-memory tile;
+// after a cluster-wide barrier the first CTA of the cluster reads the other
+// CTAs' tiles through distributed shared memory, adds them in rank order,
+// applies alpha / beta and writes D. No workspace, no atomics.
+//
+// Sums are FP32 FFMA; the order over K differs from a sequential loop only by
+// this fixed partition.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -20,9 +30,13 @@
 namespace ftcuda {
 namespace {
 
-constexpr int kStripColumns = 32;
+namespace cg = cooperative_groups;
+
+constexpr int kStripColumns = 128;
 constexpr int kWarps        = 8;
-constexpr int kRowsPerStep  = 4 * kWarps;  // K rows consumed per CTA step
+constexpr int kGroupRows    = 4;   // K rows per group (one 128-bit load of A covers them)
+constexpr int kGroupsAhead  = 2;   // groups of B kept in flight per warp
+constexpr int kMaxCluster   = 8;
 
 struct SkinnyParams {
     const float* a;
@@ -34,92 +48,140 @@ struct SkinnyParams {
     std::int64_t c_row_stride, c_col_stride;
     std::int64_t d_row_stride, d_col_stride;
     std::uint32_t m, n, k;
+    std::uint32_t groups_per_cta;  // groups of four K rows per CTA of a cluster
     float alpha, beta;
+    bool a_vector;  // A[i][k..k+3] can be fetched with one aligned 128-bit load
 };
 
 template<int kRows>
 __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) {
-    // Loads of B kept in flight per thread; fewer when the accumulators are many.
-    constexpr int kUnroll = kRows >= 16 ? 4 : 8;
-    __shared__ float4 across_warps[kWarps][kRows][8];
-    const int warp      = threadIdx.x >> 5;
-    const int lane      = threadIdx.x & 31;
-    const int row_group = lane >> 3;  // which of the 4 K rows of a warp-wide load
-    const int quad      = lane & 7;   // which 4 columns of the strip
-    const std::uint32_t col = blockIdx.x * kStripColumns + quad * 4;
-    const bool col_ok       = col < p.n;  // n % 4 == 0, so a quad is all in or all out
+    // One row of partial sums per row of A: [kRows][128 columns].
+    __shared__ float4 tile[kRows][32];
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank       = cluster.block_rank();
+    const unsigned ranks      = cluster.num_blocks();
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const std::uint32_t col = blockIdx.x * kStripColumns + lane * 4;
+    const bool col_ok       = col < p.n;  // n % 4 == 0: a lane's four columns are all in or all out
 
     float4 acc[kRows];
 #pragma unroll
     for (int i = 0; i < kRows; ++i) { acc[i] = make_float4(0.0F, 0.0F, 0.0F, 0.0F); }
 
-    const std::uint32_t first = warp * 4 + row_group;
-    for (std::uint32_t k0 = first; k0 < p.k; k0 += kRowsPerStep * kUnroll) {
-        float4 b_value[kUnroll];
+    const std::uint32_t first_group = rank * p.groups_per_cta;
+    const std::uint32_t end_group   = min(first_group + p.groups_per_cta, (p.k + kGroupRows - 1) / kGroupRows);
+    for (std::uint32_t group = first_group + warp; group < end_group; group += kWarps * kGroupsAhead) {
+        float4 b_value[kGroupsAhead][kGroupRows];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const std::uint32_t kk = k0 + u * kRowsPerStep;
-            b_value[u] = (kk < p.k && col_ok)
-                             ? __ldcs(reinterpret_cast<const float4*>(p.b + static_cast<std::int64_t>(kk) * p.b_row_stride + col))
-                             : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+        for (int u = 0; u < kGroupsAhead; ++u) {
+#pragma unroll
+            for (int r = 0; r < kGroupRows; ++r) {
+                const std::uint32_t kk = (group + u * kWarps) * kGroupRows + r;
+                b_value[u][r] = (group + u * kWarps < end_group && kk < p.k && col_ok)
+                                    ? __ldcs(reinterpret_cast<const float4*>(p.b + static_cast<std::int64_t>(kk) * p.b_row_stride + col))
+                                    : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+            }
         }
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const std::uint32_t kk = k0 + u * kRowsPerStep;
-            if (kk >= p.k) { break; }
+        for (int u = 0; u < kGroupsAhead; ++u) {
+            const std::uint32_t k0 = (group + u * kWarps) * kGroupRows;
+            if (group + u * kWarps >= end_group) { break; }
 #pragma unroll
             for (int i = 0; i < kRows; ++i) {
-                if (i < static_cast<int>(p.m)) {
-                    const float a_value =
-                        __ldg(p.a + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride);
-                    acc[i].x = fmaf(a_value, b_value[u].x, acc[i].x);
-                    acc[i].y = fmaf(a_value, b_value[u].y, acc[i].y);
-                    acc[i].z = fmaf(a_value, b_value[u].z, acc[i].z);
-                    acc[i].w = fmaf(a_value, b_value[u].w, acc[i].w);
+                if (i >= static_cast<int>(p.m)) { break; }
+                float a_value[kGroupRows];
+                const float* a_row = p.a + static_cast<std::int64_t>(i) * p.a_row_stride;
+                if (p.a_vector && k0 + kGroupRows <= p.k) {
+                    const float4 four = __ldg(reinterpret_cast<const float4*>(a_row + k0));
+                    a_value[0] = four.x;
+                    a_value[1] = four.y;
+                    a_value[2] = four.z;
+                    a_value[3] = four.w;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kGroupRows; ++r) {
+                        a_value[r] = k0 + r < p.k ? __ldg(a_row + static_cast<std::int64_t>(k0 + r) * p.a_col_stride) : 0.0F;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < kGroupRows; ++r) {
+                    acc[i].x = fmaf(a_value[r], b_value[u][r].x, acc[i].x);
+                    acc[i].y = fmaf(a_value[r], b_value[u][r].y, acc[i].y);
+                    acc[i].z = fmaf(a_value[r], b_value[u][r].z, acc[i].z);
+                    acc[i].w = fmaf(a_value[r], b_value[u][r].w, acc[i].w);
                 }
             }
         }
     }
 
-    // Fold the 4 row groups of the warp, then the 8 warps, in a fixed order.
+    // Warps fold into the shared tile one after the other.
+    for (int turn = 0; turn < kWarps; ++turn) {
+        if (warp == turn) {
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-#pragma unroll
-        for (int offset = 8; offset <= 16; offset <<= 1) {
-            acc[i].x += __shfl_xor_sync(0xFFFFFFFFU, acc[i].x, offset);
-            acc[i].y += __shfl_xor_sync(0xFFFFFFFFU, acc[i].y, offset);
-            acc[i].z += __shfl_xor_sync(0xFFFFFFFFU, acc[i].z, offset);
-            acc[i].w += __shfl_xor_sync(0xFFFFFFFFU, acc[i].w, offset);
-        }
-        if (row_group == 0) { across_warps[warp][i][quad] = acc[i]; }
-    }
-    __syncthreads();
-    // kRows * 8 quads to finish; one thread each.
-    for (int item = threadIdx.x; item < kRows * 8; item += kWarps * 32) {
-        const int i = item >> 3;
-        const int q = item & 7;
-        const std::uint32_t out_col = blockIdx.x * kStripColumns + q * 4;
-        if (i >= static_cast<int>(p.m) || out_col >= p.n) { continue; }
-        float4 sum = across_warps[0][i][q];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) {
-            const float4 next = across_warps[w][i][q];
-            sum.x += next.x;
-            sum.y += next.y;
-            sum.z += next.z;
-            sum.w += next.w;
-        }
-        const float parts[4] = {sum.x, sum.y, sum.z, sum.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float value = p.alpha * parts[j];
-            if (p.c != nullptr) {
-                value += p.beta * p.c[static_cast<std::int64_t>(i) * p.c_row_stride +
-                                      static_cast<std::int64_t>(out_col + j) * p.c_col_stride];
+            for (int i = 0; i < kRows; ++i) {
+                if (turn == 0) {
+                    tile[i][lane] = acc[i];
+                } else {
+                    float4 sum = tile[i][lane];
+                    sum.x += acc[i].x;
+                    sum.y += acc[i].y;
+                    sum.z += acc[i].z;
+                    sum.w += acc[i].w;
+                    tile[i][lane] = sum;
+                }
             }
-            p.d[static_cast<std::int64_t>(i) * p.d_row_stride + static_cast<std::int64_t>(out_col + j) * p.d_col_stride] = value;
+        }
+        __syncthreads();
+    }
+    cluster.sync();
+    if (rank == 0) {
+        for (int item = threadIdx.x; item < kRows * 32; item += kWarps * 32) {
+            const int i                 = item >> 5;
+            const int quad              = item & 31;
+            const std::uint32_t out_col = blockIdx.x * kStripColumns + quad * 4;
+            if (i >= static_cast<int>(p.m) || out_col >= p.n) { continue; }
+            float4 sum = tile[i][quad];
+            for (unsigned other = 1; other < ranks; ++other) {
+                const float4* remote = cluster.map_shared_rank(&tile[0][0], other);
+                const float4 next    = remote[i * 32 + quad];
+                sum.x += next.x;
+                sum.y += next.y;
+                sum.z += next.z;
+                sum.w += next.w;
+            }
+            const float parts[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float value = p.alpha * parts[j];
+                if (p.c != nullptr) {
+                    value += p.beta * p.c[static_cast<std::int64_t>(i) * p.c_row_stride +
+                                          static_cast<std::int64_t>(out_col + j) * p.c_col_stride];
+                }
+                p.d[static_cast<std::int64_t>(i) * p.d_row_stride + static_cast<std::int64_t>(out_col + j) * p.d_col_stride] = value;
+            }
         }
     }
+    // Nobody's shared memory may go away while the first CTA still reads it.
+    cluster.sync();
+}
+
+template<int kRows>
+cudaError_t launchRows(const LaunchState& state, const SkinnyParams& p, cudaStream_t stream) {
+    cudaLaunchConfig_t config{};
+    config.gridDim          = dim3(state.grid_x, state.grid_y, 1);
+    config.blockDim         = dim3(state.block, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream           = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id               = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 1;
+    attribute.val.clusterDim.y = state.grid_y;  // all K slices of a strip form one cluster
+    attribute.val.clusterDim.z = 1;
+    config.attrs               = &attribute;
+    config.numAttrs            = 1;
+    return cudaLaunchKernelEx(&config, skinnyGemm<kRows>, p);
 }
 
 }  // namespace
@@ -136,48 +198,64 @@ const char* supportsSkinny(const FtcudaGemmDesc& desc) {
     return nullptr;
 }
 
-int configureSkinny(LaunchState& state, char*, std::size_t) {
+int configureSkinny(LaunchState& state, char* message, std::size_t capacity) {
     const FtcudaGemmDesc& desc = state.desc;
-    state.variant              = kVariantGeneric;
-    state.grid_x               = static_cast<std::uint32_t>(ceilDiv(desc.n, kStripColumns));
-    state.grid_y               = 1;
-    state.grid_z               = 1;
-    state.block                = kWarps * 32;
-    state.smem_bytes           = 0;
-    state.splits               = 1;
-    state.workspace_bytes      = 0;
-    state.row_tile             = desc.m <= 1 ? 1 : desc.m <= 4 ? 4 : desc.m <= 8 ? 8 : desc.m <= 16 ? 16 : 32;
+    int sms                    = 0;
+    if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
+    state.variant         = kVariantGeneric;
+    state.grid_x          = static_cast<std::uint32_t>(ceilDiv(desc.n, kStripColumns));
+    state.grid_z          = 1;
+    state.block           = kWarps * 32;
+    state.smem_bytes      = 0;
+    state.splits          = 1;
+    state.workspace_bytes = 0;
+    state.row_tile        = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : desc.m <= 8 ? 8 : desc.m <= 16 ? 16 : desc.m <= 24 ? 24 : 32;
+    // CTAs per cluster (= K slices per strip): enough to put two CTAs on every
+    // SM, as long as each CTA keeps at least two groups of K rows per warp.
+    const std::uint64_t groups = ceilDiv(desc.k, kGroupRows);
+    std::uint32_t cluster      = 1;
+    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * cluster < 2ULL * sms &&
+           groups / (cluster * 2) >= 2ULL * kWarps) {
+        cluster *= 2;
+    }
+    state.grid_y      = cluster;
+    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(groups, cluster));  // groups per CTA
     return 0;
 }
 
 cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream) {
     const FtcudaGemmDesc& desc = state.desc;
     SkinnyParams p{};
-    p.a            = desc.a;
-    p.b            = desc.b;
-    p.c            = desc.c;
-    p.d            = desc.d;
-    p.a_row_stride = desc.a_row_stride;
-    p.a_col_stride = desc.a_col_stride;
-    p.b_row_stride = desc.b_row_stride;
-    p.c_row_stride = desc.c_row_stride;
-    p.c_col_stride = desc.c_col_stride;
-    p.d_row_stride = desc.d_row_stride;
-    p.d_col_stride = desc.d_col_stride;
-    p.m            = static_cast<std::uint32_t>(desc.m);
-    p.n            = static_cast<std::uint32_t>(desc.n);
-    p.k            = static_cast<std::uint32_t>(desc.k);
-    p.alpha        = desc.alpha;
-    p.beta         = desc.beta;
+    p.a              = desc.a;
+    p.b              = desc.b;
+    p.c              = desc.c;
+    p.d              = desc.d;
+    p.a_row_stride   = desc.a_row_stride;
+    p.a_col_stride   = desc.a_col_stride;
+    p.b_row_stride   = desc.b_row_stride;
+    p.c_row_stride   = desc.c_row_stride;
+    p.c_col_stride   = desc.c_col_stride;
+    p.d_row_stride   = desc.d_row_stride;
+    p.d_col_stride   = desc.d_col_stride;
+    p.m              = static_cast<std::uint32_t>(desc.m);
+    p.n              = static_cast<std::uint32_t>(desc.n);
+    p.k              = static_cast<std::uint32_t>(desc.k);
+    p.groups_per_cta = state.k_per_split;
+    p.alpha          = desc.alpha;
+    p.beta           = desc.beta;
+    p.a_vector       = desc.a_col_stride == 1 && desc.a_row_stride % 4 == 0 && reinterpret_cast<std::uintptr_t>(desc.a) % 16 == 0;
+    cudaError_t error = cudaSuccess;
     switch (state.row_tile) {
-        case 1: skinnyGemm<1><<<state.grid_x, state.block, 0, stream>>>(p); break;
-        case 4: skinnyGemm<4><<<state.grid_x, state.block, 0, stream>>>(p); break;
-        case 8: skinnyGemm<8><<<state.grid_x, state.block, 0, stream>>>(p); break;
-        case 16: skinnyGemm<16><<<state.grid_x, state.block, 0, stream>>>(p); break;
-        default: skinnyGemm<32><<<state.grid_x, state.block, 0, stream>>>(p); break;
+        case 1: error = launchRows<1>(state, p, stream); break;
+        case 2: error = launchRows<2>(state, p, stream); break;
+        case 4: error = launchRows<4>(state, p, stream); break;
+        case 8: error = launchRows<8>(state, p, stream); break;
+        case 16: error = launchRows<16>(state, p, stream); break;
+        case 24: error = launchRows<24>(state, p, stream); break;
+        default: error = launchRows<32>(state, p, stream); break;
     }
     countLaunches(1);
-    return cudaGetLastError();
+    return error;
 }
 
 }  // namespace ftcuda

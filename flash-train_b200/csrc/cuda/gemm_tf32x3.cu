@@ -137,10 +137,14 @@ __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint3
     return w;
 }
 
+// Rounds to TF32 (10 explicit mantissa bits), to nearest with ties away from
+// zero -- what cvt.rna.tf32.f32 computes -- with two full-rate integer
+// instructions: the conversion unit has a fraction of the ALU's throughput and
+// the converter warps are on the kernel's critical path. Adding half a TF32 ulp
+// to the sign-magnitude bit pattern and clearing the low 13 bits rounds the
+// magnitude; infinities stay infinities.
 __device__ __forceinline__ std::uint32_t tf32Round(float value) {
-    std::uint32_t bits;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(value));
-    return bits;
+    return (__float_as_uint(value) + 0x1000U) & 0xFFFFE000U;
 }
 
 // value = hi + lo (+ a remainder below 2^-22 |value|), both TF32.
