@@ -6,11 +6,10 @@
 // of up to 8 CTAs; the CTAs of a cluster take consecutive ranges of K, and the
 // eight warps of a CTA take interleaved groups of four K rows inside the range.
 // One warp instruction loads one K row of the strip: 32 lanes x 128 bits = 512
-// contiguous bytes, and a warp keeps two groups (eight such loads) in flight.
-// The four values A[i][k..k+3] a group needs for row i are one 128-bit load
-// whose address is the same for the whole warp (a broadcast that hits L1), so
-// the load/store unit sees about five instructions per four rows of B instead
-// of one per row and row of A.
+// contiguous bytes, and a warp keeps two to four groups (8-16 such loads) in
+// flight. The rows of A are staged in shared memory 256 K rows at a time, so the
+// four values A[i][k..k+3] a group needs for row i are one 128-bit shared load
+// with the same address for the whole warp (a broadcast).
 //
 // Reduction, all in a fixed order (results are deterministic): the warps of a
 // CTA add their partial sums one after the other into a shared-memory tile;
@@ -35,7 +34,7 @@ namespace cg = cooperative_groups;
 constexpr int kStripColumns = 128;
 constexpr int kWarps        = 8;
 constexpr int kGroupRows    = 4;   // K rows per group (one 128-bit load of A covers them)
-constexpr int kGroupsAhead  = 2;   // groups of B kept in flight per warp
+constexpr int kChunkRows    = 256; // K rows of A staged in shared memory at a time
 constexpr int kMaxCluster   = 8;
 
 struct SkinnyParams {
@@ -50,13 +49,40 @@ struct SkinnyParams {
     std::uint32_t m, n, k;
     std::uint32_t groups_per_cta;  // groups of four K rows per CTA of a cluster
     float alpha, beta;
-    bool a_vector;  // A[i][k..k+3] can be fetched with one aligned 128-bit load
 };
+
+// Streaming 128-bit load, zero when `valid` is false. Volatile, so that all
+// loads of an iteration are issued, in program order, before the first use.
+__device__ __forceinline__ float4 loadStreaming(const float* address, bool valid) {
+    float4 value;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.f32 %0, 0f00000000;\n\t"
+        "mov.f32 %1, 0f00000000;\n\t"
+        "mov.f32 %2, 0f00000000;\n\t"
+        "mov.f32 %3, 0f00000000;\n\t"
+        "@p ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];\n\t"
+        "}"
+        : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
+        : "l"(address), "r"(static_cast<int>(valid)));
+    return value;
+}
 
 template<int kRows>
 __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) {
-    // One row of partial sums per row of A: [kRows][128 columns].
-    __shared__ float4 tile[kRows][32];
+    // Groups of B kept in flight per warp: more while the accumulators are few.
+    constexpr int kAhead = kRows <= 8 ? 4 : 2;
+    // The K range of a CTA is walked in chunks of kChunkRows rows; the chunk of
+    // A that goes with it sits in shared memory, [row of A][k within chunk].
+    // After the last chunk the same memory holds the CTA's partial sums,
+    // [row of A][128 columns].
+    __shared__ float4 shared_pool[kRows * kChunkRows / 4];
+    float (*a_chunk)[kChunkRows] = reinterpret_cast<float (*)[kChunkRows]>(shared_pool);
+    float4 (*tile)[32]           = reinterpret_cast<float4 (*)[32]>(shared_pool);
+    static_assert(kChunkRows >= 128, "the partial-sum tile must fit the pool");
+
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank       = cluster.block_rank();
     const unsigned ranks      = cluster.num_blocks();
@@ -70,51 +96,55 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
 #pragma unroll
     for (int i = 0; i < kRows; ++i) { acc[i] = make_float4(0.0F, 0.0F, 0.0F, 0.0F); }
 
-    const std::uint32_t first_group = rank * p.groups_per_cta;
-    const std::uint32_t end_group   = min(first_group + p.groups_per_cta, (p.k + kGroupRows - 1) / kGroupRows);
-    for (std::uint32_t group = first_group + warp; group < end_group; group += kWarps * kGroupsAhead) {
-        float4 b_value[kGroupsAhead][kGroupRows];
-#pragma unroll
-        for (int u = 0; u < kGroupsAhead; ++u) {
-#pragma unroll
-            for (int r = 0; r < kGroupRows; ++r) {
-                const std::uint32_t kk = (group + u * kWarps) * kGroupRows + r;
-                b_value[u][r] = (group + u * kWarps < end_group && kk < p.k && col_ok)
-                                    ? __ldcs(reinterpret_cast<const float4*>(p.b + static_cast<std::int64_t>(kk) * p.b_row_stride + col))
-                                    : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-            }
+    const std::uint32_t k_begin = rank * p.groups_per_cta * kGroupRows;
+    const std::uint32_t k_end   = min(k_begin + p.groups_per_cta * kGroupRows, p.k);
+    for (std::uint32_t chunk = k_begin; chunk < k_end; chunk += kChunkRows) {
+        // Stage A[0..m)[chunk .. chunk + kChunkRows): zeros past the end of K.
+        // Consecutive threads walk the unit-stride direction of A.
+        __syncthreads();
+        const bool k_fastest = p.a_col_stride == 1;
+        for (int item = threadIdx.x; item < kRows * kChunkRows; item += kWarps * 32) {
+            const int i  = k_fastest ? item / kChunkRows : item % kRows;
+            const int kc = k_fastest ? item % kChunkRows : item / kRows;
+            const std::uint32_t kk = chunk + kc;
+            a_chunk[i][kc] = (i < static_cast<int>(p.m) && kk < k_end)
+                                 ? __ldg(p.a + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride)
+                                 : 0.0F;
         }
+        __syncthreads();
+        constexpr int kChunkGroups = kChunkRows / kGroupRows;
+        for (int group = warp; group < kChunkGroups; group += kWarps * kAhead) {
+            float4 b_value[kAhead][kGroupRows];
 #pragma unroll
-        for (int u = 0; u < kGroupsAhead; ++u) {
-            const std::uint32_t k0 = (group + u * kWarps) * kGroupRows;
-            if (group + u * kWarps >= end_group) { break; }
-#pragma unroll
-            for (int i = 0; i < kRows; ++i) {
-                if (i >= static_cast<int>(p.m)) { break; }
-                float a_value[kGroupRows];
-                const float* a_row = p.a + static_cast<std::int64_t>(i) * p.a_row_stride;
-                if (p.a_vector && k0 + kGroupRows <= p.k) {
-                    const float4 four = __ldg(reinterpret_cast<const float4*>(a_row + k0));
-                    a_value[0] = four.x;
-                    a_value[1] = four.y;
-                    a_value[2] = four.z;
-                    a_value[3] = four.w;
-                } else {
-#pragma unroll
-                    for (int r = 0; r < kGroupRows; ++r) {
-                        a_value[r] = k0 + r < p.k ? __ldg(a_row + static_cast<std::int64_t>(k0 + r) * p.a_col_stride) : 0.0F;
-                    }
-                }
+            for (int u = 0; u < kAhead; ++u) {
 #pragma unroll
                 for (int r = 0; r < kGroupRows; ++r) {
-                    acc[i].x = fmaf(a_value[r], b_value[u][r].x, acc[i].x);
-                    acc[i].y = fmaf(a_value[r], b_value[u][r].y, acc[i].y);
-                    acc[i].z = fmaf(a_value[r], b_value[u][r].z, acc[i].z);
-                    acc[i].w = fmaf(a_value[r], b_value[u][r].w, acc[i].w);
+                    const std::uint32_t kk = chunk + (group + u * kWarps) * kGroupRows + r;
+                    b_value[u][r] = loadStreaming(p.b + static_cast<std::int64_t>(kk) * p.b_row_stride + col,
+                                                  group + u * kWarps < kChunkGroups && kk < k_end && col_ok);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int kc = (group + u * kWarps) * kGroupRows;
+                if (group + u * kWarps >= kChunkGroups) { break; }
+#pragma unroll
+                for (int i = 0; i < kRows; ++i) {
+                    // One 128-bit shared load, the same address for the whole warp.
+                    const float4 four      = *reinterpret_cast<const float4*>(&a_chunk[i][kc]);
+                    const float a_value[4] = {four.x, four.y, four.z, four.w};
+#pragma unroll
+                    for (int r = 0; r < kGroupRows; ++r) {
+                        acc[i].x = fmaf(a_value[r], b_value[u][r].x, acc[i].x);
+                        acc[i].y = fmaf(a_value[r], b_value[u][r].y, acc[i].y);
+                        acc[i].z = fmaf(a_value[r], b_value[u][r].z, acc[i].z);
+                        acc[i].w = fmaf(a_value[r], b_value[u][r].w, acc[i].w);
+                    }
                 }
             }
         }
     }
+    __syncthreads();  // the pool changes its role
 
     // Warps fold into the shared tile one after the other.
     for (int turn = 0; turn < kWarps; ++turn) {
@@ -243,7 +273,6 @@ cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream) {
     p.groups_per_cta = state.k_per_split;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
-    p.a_vector       = desc.a_col_stride == 1 && desc.a_row_stride % 4 == 0 && reinterpret_cast<std::uintptr_t>(desc.a) % 16 == 0;
     cudaError_t error = cudaSuccess;
     switch (state.row_tile) {
         case 1: error = launchRows<1>(state, p, stream); break;
