@@ -44,6 +44,9 @@ WORKLOADS = {
     "gemm_fp32_16384x4096x14336": (16384, 4096, 14336, 3, "rsqrt_k", 1.0, 0.0, False),
     "gemm_fp32_4096x4096x4096_addend": (4096, 4096, 4096, 1, "one", 1.5, 0.5, True),
 }
+# Tall-K workload: K sharded over the ranks, partial products summed by an NCCL reduce-scatter.
+KSPLIT_WORKLOAD = "gemm_fp32_2048x262144x2048_ksplit"
+KSPLIT_SHAPE = (2048, 262144, 2048)
 DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
 CPU_SAMPLE_ROWS = 2048  # rows of A per CPU-baseline step
 
@@ -232,13 +235,86 @@ def plan_reuse_overhead(capi, torch, device) -> dict:
             "note": "host time of 1000 ftrainPlanExecutePrimitive calls through ctypes (no sync inside), m=n=k=1024"}
 
 
+def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
+    """m=n=2048, k=262144, U(-1,1): rank r holds A[:, K_r] and B[K_r, :] (contiguous per rank),
+    computes a full 2048x2048 partial and the partials are reduce-scattered (rows of D)."""
+    import torch.distributed as dist
+
+    from flash_train import sharded
+
+    m, k, n = KSPLIT_SHAPE
+    distributed = world > 1
+    k_start, k_stop = sharded.k_range(k, world, rank)
+    generator = torch.Generator(device=device).manual_seed(4 + rank)
+    a = torch.rand(m, k_stop - k_start, device=device, generator=generator) * 2 - 1
+    b = torch.rand(k_stop - k_start, n, device=device, generator=generator) * 2 - 1
+    if distributed:
+        gemm = sharded.KShardedGemm(m, n, k)
+        out = torch.empty(m // world, n, device=device)
+
+        def step():
+            gemm(a, b, None, 1.0, 0.0, out=out)
+        primitive = "K-sharded: local Plan + ncclReduceScatter"
+    else:
+        gemm = sharded.RowShardedGemm(m, 1, 0)
+        out = torch.empty(m, n, device=device)
+
+        def step():
+            gemm(a, b, None, 1.0, 0.0, out=out)
+        primitive = "single GPU"
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(options.warmup):
+        step()
+    barrier()
+    start_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = capi.launch_count()
+    with ClockSampler(local_rank) as sampler:
+        start_event.record()
+        for _ in range(options.steps):
+            step()
+        end_event.record()
+        barrier()
+        elapsed_ms = start_event.elapsed_time(end_event)
+    launches = capi.launch_count() - launches_before
+    if distributed:
+        slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(slowest.item())
+    if rank == 0:
+        ms_per_step = elapsed_ms / options.steps
+        value = 2.0 * m * n * k / (ms_per_step * 1e-3) / 1e12
+        peaks = measured_peaks()
+        tensor_peak = peaks["bf16_tflops_sustained"] / 6.0
+        line = {
+            "metric": "fp32_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": options.steps,
+            "warmup": options.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": options.workload, "m": m, "k": k, "n": n, "k_per_gpu": k_stop - k_start,
+                       "partition": "K ranges per GPU; partial D summed by reduce-scatter over NVLink", "primitive": primitive,
+                       "l2": "A and B shards (2 x 2 GiB in total) exceed the 126 MB L2"},
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": tensor_peak, "unit": "TFLOP/s",
+                         "frac": value / world / tensor_peak, "traffic": None,
+                         "peak_source": f"{peaks['source']} bf16_tflops_sustained / 6"},
+            "clocks": sampler.summary(), "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD])
     parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
     parser.add_argument("--primitive", default=None,
                         help="run this Primitive of the Plan instead of index 0 (per-primitive tier), e.g. Fp32Gemm")
@@ -267,6 +343,9 @@ def main() -> int:
     from flash_train import capi  # fails loudly if libflash_train.so is missing
     import flash_train.torch as ft_torch
     from flash_train.capi import GemmBinding, null_operand, tensor_operand
+
+    if options.workload == KSPLIT_WORKLOAD:
+        return run_k_split(options, torch, capi, world, rank, local_rank, device)
 
     m, k, n, *_ = WORKLOADS[options.workload]
     if m % world != 0:
