@@ -48,6 +48,7 @@ struct SkinnyParams {
     std::int64_t d_row_stride, d_col_stride;
     std::uint32_t m, n, k;
     std::uint32_t groups_per_cta;  // groups of four K rows per CTA of a cluster
+    std::uint32_t rows_per_z;      // rows of A per blockIdx.z slab
     float alpha, beta;
 };
 
@@ -92,6 +93,11 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
     const std::uint32_t col = blockIdx.x * kStripColumns + lane * 4;
     const bool col_ok       = col < p.n;  // n % 4 == 0: a lane's four columns are all in or all out
 
+    // blockIdx.z selects a slab of up to kRows rows of A (and of C and D).
+    const std::uint32_t row0    = blockIdx.z * p.rows_per_z;
+    const int slab_rows         = static_cast<int>(min(p.rows_per_z, p.m - row0));
+    const float* const a_slab   = p.a + static_cast<std::int64_t>(row0) * p.a_row_stride;
+
     float4 acc[kRows];
 #pragma unroll
     for (int i = 0; i < kRows; ++i) { acc[i] = make_float4(0.0F, 0.0F, 0.0F, 0.0F); }
@@ -107,8 +113,8 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
             const int i  = k_fastest ? item / kChunkRows : item % kRows;
             const int kc = k_fastest ? item % kChunkRows : item / kRows;
             const std::uint32_t kk = chunk + kc;
-            a_chunk[i][kc] = (i < static_cast<int>(p.m) && kk < k_end)
-                                 ? __ldg(p.a + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride)
+            a_chunk[i][kc] = (i < slab_rows && kk < k_end)
+                                 ? __ldg(a_slab + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride)
                                  : 0.0F;
         }
         __syncthreads();
@@ -171,7 +177,8 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
             const int i                 = item >> 5;
             const int quad              = item & 31;
             const std::uint32_t out_col = blockIdx.x * kStripColumns + quad * 4;
-            if (i >= static_cast<int>(p.m) || out_col >= p.n) { continue; }
+            if (i >= slab_rows || out_col >= p.n) { continue; }
+            const std::int64_t out_row = static_cast<std::int64_t>(row0) + i;
             float4 sum = tile[i][quad];
             for (unsigned other = 1; other < ranks; ++other) {
                 const float4* remote = cluster.map_shared_rank(&tile[0][0], other);
@@ -186,10 +193,9 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
             for (int j = 0; j < 4; ++j) {
                 float value = p.alpha * parts[j];
                 if (p.c != nullptr) {
-                    value += p.beta * p.c[static_cast<std::int64_t>(i) * p.c_row_stride +
-                                          static_cast<std::int64_t>(out_col + j) * p.c_col_stride];
+                    value += p.beta * p.c[out_row * p.c_row_stride + static_cast<std::int64_t>(out_col + j) * p.c_col_stride];
                 }
-                p.d[static_cast<std::int64_t>(i) * p.d_row_stride + static_cast<std::int64_t>(out_col + j) * p.d_col_stride] = value;
+                p.d[out_row * p.d_row_stride + static_cast<std::int64_t>(out_col + j) * p.d_col_stride] = value;
             }
         }
     }
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
 template<int kRows>
 cudaError_t launchRows(const LaunchState& state, const SkinnyParams& p, cudaStream_t stream) {
     cudaLaunchConfig_t config{};
-    config.gridDim          = dim3(state.grid_x, state.grid_y, 1);
+    config.gridDim          = dim3(state.grid_x, state.grid_y, state.grid_z);
     config.blockDim         = dim3(state.block, 1, 1);
     config.dynamicSmemBytes = 0;
     config.stream           = stream;
@@ -234,17 +240,21 @@ int configureSkinny(LaunchState& state, char* message, std::size_t capacity) {
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
     state.variant         = kVariantGeneric;
     state.grid_x          = static_cast<std::uint32_t>(ceilDiv(desc.n, kStripColumns));
-    state.grid_z          = 1;
     state.block           = kWarps * 32;
     state.smem_bytes      = 0;
     state.splits          = 1;
     state.workspace_bytes = 0;
-    state.row_tile        = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : desc.m <= 8 ? 8 : desc.m <= 16 ? 16 : desc.m <= 24 ? 24 : 32;
+    // Up to eight rows of A per CTA; more rows become slabs along blockIdx.z. The
+    // slabs of a strip run side by side and read the same rows of B, which
+    // therefore come from HBM once and from L2 for the other slabs. Eight rows
+    // keep the accumulators small enough for sixteen loads in flight per warp.
+    state.row_tile = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : 8;
+    state.grid_z   = static_cast<std::uint32_t>(ceilDiv(desc.m, state.row_tile));
     // CTAs per cluster (= K slices per strip): enough to put two CTAs on every
     // SM, as long as each CTA keeps at least two groups of K rows per warp.
     const std::uint64_t groups = ceilDiv(desc.k, kGroupRows);
     std::uint32_t cluster      = 1;
-    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * cluster < 2ULL * sms &&
+    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * state.grid_z * cluster < 2ULL * sms &&
            groups / (cluster * 2) >= 2ULL * kWarps) {
         cluster *= 2;
     }
@@ -271,6 +281,7 @@ cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream) {
     p.n              = static_cast<std::uint32_t>(desc.n);
     p.k              = static_cast<std::uint32_t>(desc.k);
     p.groups_per_cta = state.k_per_split;
+    p.rows_per_z     = state.row_tile;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
     cudaError_t error = cudaSuccess;
@@ -278,10 +289,7 @@ cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream) {
         case 1: error = launchRows<1>(state, p, stream); break;
         case 2: error = launchRows<2>(state, p, stream); break;
         case 4: error = launchRows<4>(state, p, stream); break;
-        case 8: error = launchRows<8>(state, p, stream); break;
-        case 16: error = launchRows<16>(state, p, stream); break;
-        case 24: error = launchRows<24>(state, p, stream); break;
-        default: error = launchRows<32>(state, p, stream); break;
+        default: error = launchRows<8>(state, p, stream); break;
     }
     countLaunches(1);
     return error;

@@ -84,9 +84,6 @@ constexpr int kAColumn         = 2 * kTileN;   // A operands: 64 columns per sta
 constexpr int kHalfColumns     = kTileN / 2;   // columns per epilogue warp
 constexpr int kPieces          = kHalfColumns / 16;
 
-// Rows of M tiles walked together so that concurrently running CTAs share B
-// panels in L2.
-constexpr std::uint32_t kGroupM = 16;
 
 struct TensorParams {
     const float* c;
@@ -97,6 +94,7 @@ struct TensorParams {
     std::uint32_t tiles_m, tiles_n;
     std::uint32_t splits, k_per_split;
     std::uint32_t chunk_k_blocks;
+    std::uint32_t band_m_tiles;  // M tiles walked together, so that concurrent CTAs share B panels in L2
     float alpha, beta;
     float* partials;  // non-null: raw sums to partials[split][m][n]
     int* status;
@@ -125,10 +123,10 @@ __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint3
     WorkItem w;
     w.split                   = item / tiles;
     const std::uint32_t tile  = item - w.split * tiles;
-    const std::uint32_t band  = tile / (kGroupM * p.tiles_n);
-    const std::uint32_t first = band * kGroupM;
-    const std::uint32_t rows  = min(kGroupM, p.tiles_m - first);
-    const std::uint32_t rest  = tile - band * kGroupM * p.tiles_n;
+    const std::uint32_t band  = tile / (p.band_m_tiles * p.tiles_n);
+    const std::uint32_t first = band * p.band_m_tiles;
+    const std::uint32_t rows  = min(p.band_m_tiles, p.tiles_m - first);
+    const std::uint32_t rest  = tile - band * p.band_m_tiles * p.tiles_n;
     w.tile_m                  = (first + rest % rows) * kTileM;
     w.tile_n                  = (rest / rows) * kTileN;
     w.k_begin                 = w.split * p.k_per_split;
@@ -515,6 +513,18 @@ std::uint32_t chunkKBlocks() {
     return 4;
 }
 
+// Output tiles are walked in bands of this many M tiles (all N tiles of a band
+// before the next band): every band re-reads B once from HBM while its A
+// panels (band x 128 rows x K) stay in L2. FTCUDA_TF32_BAND_M_TILES overrides.
+std::uint32_t bandMTiles() {
+    const char* text = std::getenv("FTCUDA_TF32_BAND_M_TILES");
+    if (text != nullptr) {
+        const long value = std::strtol(text, nullptr, 10);
+        if (value >= 1 && value <= 4096) { return static_cast<std::uint32_t>(value); }
+    }
+    return 16;
+}
+
 }  // namespace
 
 const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
@@ -591,6 +601,7 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     p.splits         = state.splits;
     p.k_per_split    = state.k_per_split;
     p.chunk_k_blocks = state.chunk_k_blocks;
+    p.band_m_tiles   = bandMTiles();
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
     p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
