@@ -48,6 +48,12 @@ WORKLOADS = {
 KSPLIT_WORKLOAD = "gemm_fp32_2048x262144x2048_ksplit"
 KSPLIT_SHAPE = (2048, 262144, 2048)
 DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on one GPU, from the ncu
+# captures summarised under profiles/ (a benchmark run cannot profile itself).
+MEASURED_DRAM_TRAFFIC = {
+    ("gemm_fp32_16384x4096x14336", "Fp32Gemm3xTf32", 1): 3210738432 + 925277440,
+    ("gemm_fp32_4096x4096x4096_addend", "Fp32Gemm3xTf32", 1): 383589120 + 55749888,
+}
 CPU_SAMPLE_ROWS = 2048  # rows of A per CPU-baseline step
 
 
@@ -440,7 +446,9 @@ def main() -> int:
     per_gpu = value / world
     if primitive.startswith("Fp32Gemm3xTf32"):
         roofline = {"bound": "tensor", "achieved": per_gpu, "peak": tensor_peak, "unit": "TFLOP/s",
-                    "frac": per_gpu / tensor_peak, "traffic": None,
+                    "frac": per_gpu / tensor_peak,
+                    "traffic": MEASURED_DRAM_TRAFFIC.get((options.workload, primitive, world)),
+                    "algorithmic_bytes": 4 * (m * k + k * n + m * n * (2 if c is not None else 1)),
                     "peak_source": f"{peaks['source']} bf16_tflops_sustained / 6 (TF32 = BF16/2; 3 MMAs per product)",
                     "kernel": "tensorGemm3xTf32", "ms_per_launch": ms_per_step}
     else:
