@@ -1,21 +1,32 @@
 // Exact-FP32 GEMM for very few rows of A (m <= 32): D = alpha * A * B + beta * C
-// where the whole cost is reading B once. HBM-bound; algorithmic traffic
+// where the whole cost is reading B once. HBM-bound up to about 16 rows (beyond
+// that the FP32 pipe catches up); algorithmic traffic
 // 4 * (k * n + m * k + m * n [+ m * n]) bytes, of which k * n dominates.
 //
 // Work split. A strip of 128 columns of B belongs to one thread-block CLUSTER
-// of up to 8 CTAs; the CTAs of a cluster take consecutive ranges of K, and the
-// eight warps of a CTA take interleaved groups of four K rows inside the range.
-// One warp instruction loads one K row of the strip: 32 lanes x 128 bits = 512
-// contiguous bytes, and a warp keeps two to four groups (8-16 such loads) in
-// flight. The rows of A are staged in shared memory 256 K rows at a time, so the
-// four values A[i][k..k+3] a group needs for row i are one 128-bit shared load
-// with the same address for the whole warp (a broadcast).
+// of up to 8 CTAs; the CTAs of a cluster take consecutive ranges of K (whole
+// boxes of 32 rows). Inside a CTA the range streams through a ring of
+// shared-memory slots filled by TMA, one 32 x 128 box (16 KiB) per copy, so
+// that 64-144 KiB per CTA are in flight without holding registers. Warp 0
+// issues the copies; all eight warps consume: each takes four rows of every
+// box, one 128-bit shared load per row (32 lanes x 16 bytes = the 512-byte row,
+// conflict free), and releases the slot as soon as the values are in registers.
+// The rows of A that go with the range are staged in shared memory 128 K values
+// at a time by asynchronous copies, one stage ahead, so the four values
+// A[i][k..k+3] a warp needs for row i are one 128-bit shared load with the same
+// address for the whole warp (a broadcast). All rows of A (templates for 1, 2,
+// 4, 8, 16, 24, 32) are accumulated by the same CTA, so B leaves HBM once.
 //
 // Reduction, all in a fixed order (results are deterministic): the warps of a
-// CTA add their partial sums one after the other into a shared-memory tile;
-// after a cluster-wide barrier the first CTA of the cluster reads the other
-// CTAs' tiles through distributed shared memory, adds them in rank order,
-// applies alpha / beta and writes D. No workspace, no atomics.
+// CTA park their sums in shared memory and each element is summed in warp
+// order; each CTA of the cluster owns a share of the strip's columns and
+// receives the other CTAs' sums for them through distributed shared memory;
+// after one cluster barrier the owner adds them in rank order, applies
+// alpha / beta and writes D. No workspace, no atomics.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets the CTA's
+// abort flag, the CTA skips its remaining work, still meets the cluster
+// barriers and reports through the status word (D is then undefined).
 //
 // Sums are FP32 FFMA; the order over K differs from a sequential loop only by
 // this fixed partition.
@@ -25,6 +36,7 @@
 #include <cstdint>
 
 #include "gemm_kernels.hpp"
+#include "ptx.cuh"
 
 namespace ftcuda {
 namespace {
@@ -33,9 +45,25 @@ namespace cg = cooperative_groups;
 
 constexpr int kStripColumns = 128;
 constexpr int kWarps        = 8;
-constexpr int kGroupRows    = 4;   // K rows per group (one 128-bit load of A covers them)
-constexpr int kChunkRows    = 256; // K rows of A staged in shared memory at a time
+constexpr int kThreads      = kWarps * 32;
+constexpr int kBoxRows      = 32;                 // K rows per TMA box: four per consumer warp
+constexpr int kBoxBytes     = kBoxRows * kStripColumns * 4;
 constexpr int kMaxCluster   = 8;
+static_assert(kBoxRows == kWarps * 4, "a consumer warp takes four rows of a box");
+
+// Per row count: up to 16 rows of A two CTAs share an SM (five boxes in flight
+// each); 24 and 32 rows need most of the register file, one CTA per SM with ten
+// boxes in flight.
+__host__ __device__ constexpr int slots(int rows) { return rows <= 16 ? 5 : 10; }
+constexpr int kStageRows = 128;  // K values of each row of A per stage (four boxes); two stages in shared memory
+__host__ __device__ constexpr int ctasPerSm(int rows) { return rows <= 16 ? 2 : 1; }
+// Shared memory: ring | two A stages | received partial sums | barriers.
+__host__ __device__ constexpr int ringBytes(int rows) { return slots(rows) * kBoxBytes; }
+__host__ __device__ constexpr int stageBytes(int rows) { return 2 * rows * kStageRows * 4; }
+__host__ __device__ constexpr int receiveBytes(int rows) { return rows * kStripColumns * 4; }
+constexpr std::uint32_t smemBytes(int rows) {
+    return 127 + ringBytes(rows) + stageBytes(rows) + receiveBytes(rows) + 2 * slots(rows) * 8;
+}
 
 struct SkinnyParams {
     const float* a;
@@ -47,150 +75,252 @@ struct SkinnyParams {
     std::int64_t c_row_stride, c_col_stride;
     std::int64_t d_row_stride, d_col_stride;
     std::uint32_t m, n, k;
-    std::uint32_t groups_per_cta;  // groups of four K rows per CTA of a cluster
+    std::uint32_t rows_per_cta;    // K rows per CTA of a cluster, a multiple of the box
     std::uint32_t rows_per_z;      // rows of A per blockIdx.z slab
     float alpha, beta;
+    int* status;  // mapped host word, set when a wait ran out
 };
 
-// Streaming 128-bit load, zero when `valid` is false. Volatile, so that all
-// loads of an iteration are issued, in program order, before the first use.
-__device__ __forceinline__ float4 loadStreaming(const float* address, bool valid) {
-    float4 value;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.f32 %0, 0f00000000;\n\t"
-        "mov.f32 %1, 0f00000000;\n\t"
-        "mov.f32 %2, 0f00000000;\n\t"
-        "mov.f32 %3, 0f00000000;\n\t"
-        "@p ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];\n\t"
-        "}"
-        : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
-        : "l"(address), "r"(static_cast<int>(valid)));
-    return value;
+// The cluster barrier in its two halves; every thread of every CTA executes both.
+__device__ __forceinline__ void clusterArrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void clusterWait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// Asynchronous copies global -> shared that hold no registers while in flight;
+// `bytes` (0 ... size) are read, the rest of the destination is zero-filled.
+__device__ __forceinline__ void copyAsync4(void* destination, const float* source, std::uint32_t bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smemAddress(destination)), "l"(source), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void copyAsync16(void* destination, const float* source, std::uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smemAddress(destination)), "l"(source), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copyAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copyAsyncWaitAll() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ float4 add4(float4 x, float4 y) { return make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w); }
 
 template<int kRows>
-__global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) {
-    // Groups of B kept in flight per warp: more while the accumulators are few.
-    constexpr int kAhead = kRows <= 8 ? 4 : 2;
-    // The K range of a CTA is walked in chunks of kChunkRows rows; the chunk of
-    // A that goes with it sits in shared memory, [row of A][k within chunk].
-    // After the last chunk the same memory holds the CTA's partial sums,
-    // [row of A][128 columns].
-    __shared__ float4 shared_pool[kRows * kChunkRows / 4];
-    float (*a_chunk)[kChunkRows] = reinterpret_cast<float (*)[kChunkRows]>(shared_pool);
-    float4 (*tile)[32]           = reinterpret_cast<float4 (*)[32]>(shared_pool);
-    static_assert(kChunkRows >= 128, "the partial-sum tile must fit the pool");
+__global__ void __launch_bounds__(kThreads, ctasPerSm(kRows))
+skinnyGemm(const __grid_constant__ CUtensorMap map_b, const SkinnyParams p) {
+    constexpr int kSlots = slots(kRows);
+    static_assert(kStageRows % kBoxRows == 0, "stages hold whole boxes");
+    static_assert(kWarps * kRows * kStripColumns * 4 <= ringBytes(kRows), "the per-warp partial sums reuse the ring");
+
+    extern __shared__ unsigned char smem_raw[];
+    const std::uint32_t align_offset = (128 - (smemAddress(smem_raw) & 127)) & 127;
+    unsigned char* ring              = smem_raw + align_offset;
+    // [stage parity][row of A][k within the stage]
+    float (*a_stage)[kRows][kStageRows] = reinterpret_cast<float (*)[kRows][kStageRows]>(ring + ringBytes(kRows));
+    // [rank of the sender][row][quad within the receiver's share of the strip]
+    float4* received                 = reinterpret_cast<float4*>(ring + ringBytes(kRows) + stageBytes(kRows));
+    std::uint64_t* full  = reinterpret_cast<std::uint64_t*>(ring + ringBytes(kRows) + stageBytes(kRows) + receiveBytes(kRows));
+    std::uint64_t* empty = full + kSlots;
+    // After the K loop the ring holds every warp's partial sums: [warp][row][quad].
+    float4 (*part)[kRows][32] = reinterpret_cast<float4 (*)[kRows][32]>(ring);
+    __shared__ int abort_flag;
+    __shared__ int never_abort;
 
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank       = cluster.block_rank();
-    const unsigned ranks      = cluster.num_blocks();
+    const unsigned ranks      = cluster.num_blocks();  // 1, 2, 4 or 8
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const std::uint32_t col = blockIdx.x * kStripColumns + lane * 4;
-    const bool col_ok       = col < p.n;  // n % 4 == 0: a lane's four columns are all in or all out
+    const std::uint32_t strip_col = blockIdx.x * kStripColumns;
 
     // blockIdx.z selects a slab of up to kRows rows of A (and of C and D).
-    const std::uint32_t row0    = blockIdx.z * p.rows_per_z;
-    const int slab_rows         = static_cast<int>(min(p.rows_per_z, p.m - row0));
-    const float* const a_slab   = p.a + static_cast<std::int64_t>(row0) * p.a_row_stride;
+    const std::uint32_t row0  = blockIdx.z * p.rows_per_z;
+    const int slab_rows       = static_cast<int>(min(p.rows_per_z, p.m - row0));
+    const float* const a_slab = p.a + static_cast<std::int64_t>(row0) * p.a_row_stride;
+
+    // K range of this CTA: whole boxes of 32 rows.
+    const std::uint32_t k_begin = min(rank * p.rows_per_cta, p.k);
+    const std::uint32_t k_end   = min(k_begin + p.rows_per_cta, p.k);
+    const std::uint32_t boxes   = (k_end - k_begin + kBoxRows - 1) / kBoxRows;
+
+    if (threadIdx.x == 0) {
+        abort_flag  = 0;
+        never_abort = 0;
+        for (int s = 0; s < kSlots; ++s) {
+            mbarrierInit(&full[s], 1);
+            mbarrierInit(&empty[s], kWarps);
+        }
+        fenceBarrierInit();
+        prefetchTensorMap(&map_b);
+    }
+    __syncthreads();
+    // First half of a cluster barrier whose only purpose is "every CTA of the
+    // cluster runs": its second half sits in front of the first remote store.
+    clusterArrive();
 
     float4 acc[kRows];
 #pragma unroll
     for (int i = 0; i < kRows; ++i) { acc[i] = make_float4(0.0F, 0.0F, 0.0F, 0.0F); }
 
-    const std::uint32_t k_begin = rank * p.groups_per_cta * kGroupRows;
-    const std::uint32_t k_end   = min(k_begin + p.groups_per_cta * kGroupRows, p.k);
-    for (std::uint32_t chunk = k_begin; chunk < k_end; chunk += kChunkRows) {
-        // Stage A[0..m)[chunk .. chunk + kChunkRows): zeros past the end of K.
-        // Consecutive threads walk the unit-stride direction of A.
-        __syncthreads();
-        const bool k_fastest = p.a_col_stride == 1;
-        for (int item = threadIdx.x; item < kRows * kChunkRows; item += kWarps * 32) {
-            const int i  = k_fastest ? item / kChunkRows : item % kRows;
-            const int kc = k_fastest ? item % kChunkRows : item / kRows;
-            const std::uint32_t kk = chunk + kc;
-            a_chunk[i][kc] = (i < slab_rows && kk < k_end)
-                                 ? __ldg(a_slab + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride)
-                                 : 0.0F;
+    // Warp 0 doubles as the producer. Before the loop it fills every slot; inside
+    // the loop, once it has taken box b into registers, it waits until all warps
+    // have released box b-1 (they release right after their loads, so this is
+    // short) and refills that slot with box b-1+kSlots.
+    std::uint32_t issued = 0;  // boxes handed to TMA (tracked by warp 0)
+    auto issue_box = [&](std::uint32_t box) {
+        const std::uint32_t s = box % kSlots;
+        mbarrierArriveExpectTx(&full[s], kBoxBytes);
+        tmaLoad2d(ring + s * kBoxBytes, &map_b, &full[s], static_cast<std::int32_t>(strip_col),
+                  static_cast<std::int32_t>(k_begin + box * kBoxRows));
+    };
+    if (warp == 0) {
+        issued = min(boxes, static_cast<std::uint32_t>(kSlots));
+        if (lane == 0) {
+            for (std::uint32_t box = 0; box < issued; ++box) { issue_box(box); }
         }
-        __syncthreads();
-        constexpr int kChunkGroups = kChunkRows / kGroupRows;
-        for (int group = warp; group < kChunkGroups; group += kWarps * kAhead) {
-            float4 b_value[kAhead][kGroupRows];
-#pragma unroll
-            for (int u = 0; u < kAhead; ++u) {
-#pragma unroll
-                for (int r = 0; r < kGroupRows; ++r) {
-                    const std::uint32_t kk = chunk + (group + u * kWarps) * kGroupRows + r;
-                    b_value[u][r] = loadStreaming(p.b + static_cast<std::int64_t>(kk) * p.b_row_stride + col,
-                                                  group + u * kWarps < kChunkGroups && kk < k_end && col_ok);
+        __syncwarp();
+    }
+    {
+        // The rows of A for this CTA's K range are staged kStageRows at a time with
+        // asynchronous copies, one stage ahead of the boxes being multiplied.
+        const bool vector_copies = p.a_col_stride == 1 && (p.a_row_stride & 3) == 0 &&
+                                   (reinterpret_cast<std::uintptr_t>(a_slab) & 15) == 0;
+        auto stage_in = [&](std::uint32_t stage_begin, int parity) {
+            if (vector_copies) {
+                // Four consecutive K values per copy; k_begin is a multiple of 32, so they are 16-byte aligned.
+                for (int item = threadIdx.x; item < kRows * (kStageRows / 4); item += kThreads) {
+                    const int i            = item / (kStageRows / 4);
+                    const int kc           = (item % (kStageRows / 4)) * 4;
+                    const std::uint32_t kk = stage_begin + kc;
+                    const bool valid       = i < slab_rows && kk < k_end;
+                    const std::uint32_t bytes = valid ? min(k_end - kk, 4U) * 4U : 0U;
+                    copyAsync16(&a_stage[parity][i][kc], valid ? a_slab + static_cast<std::int64_t>(i) * p.a_row_stride + kk : p.a, bytes);
+                }
+            } else {
+                // Any strides: one element per copy, consecutive threads along the unit-stride direction of A.
+                const bool k_fastest = p.a_col_stride == 1;
+                for (int item = threadIdx.x; item < kRows * kStageRows; item += kThreads) {
+                    const int i            = k_fastest ? item / kStageRows : item % kRows;
+                    const int kc           = k_fastest ? item % kStageRows : item / kRows;
+                    const std::uint32_t kk = stage_begin + kc;
+                    const bool valid       = i < slab_rows && kk < k_end;
+                    copyAsync4(&a_stage[parity][i][kc],
+                               valid ? a_slab + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride : p.a,
+                               valid ? 4U : 0U);
                 }
             }
+            copyAsyncCommit();
+        };
+        bool ok = true;
+        if (k_begin < k_end) { stage_in(k_begin, 0); }
+        int parity = 0;
+        for (std::uint32_t stage_begin = k_begin; stage_begin < k_end; stage_begin += kStageRows, parity ^= 1) {
+            // This thread's copies of the stage have landed; after the barrier so have
+            // everybody's, and every warp is done with the other stage.
+            copyAsyncWaitAll();
+            __syncthreads();
+            if (stage_begin + kStageRows < k_end) { stage_in(stage_begin + kStageRows, parity ^ 1); }
+            const std::uint32_t first_box = (stage_begin - k_begin) / kBoxRows;
+            const std::uint32_t last_box  = min(first_box + kStageRows / kBoxRows, boxes);
+            for (std::uint32_t box = first_box; box < last_box && ok; ++box) {
+                const std::uint32_t s = box % kSlots;
+                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&full[s], (box / kSlots) & 1, &abort_flag));
+                if (!ok) {
+                    abort_flag = 1;
+                    break;
+                }
+                // Warp w owns rows 4w..4w+3 of the box: one 128-bit load per row,
+                // 32 lanes x 16 bytes = the 512-byte row.
+                const unsigned char* rows = ring + s * kBoxBytes + (warp * 4) * (kStripColumns * 4) + lane * 16;
+                const int kc              = static_cast<int>(box - first_box) * kBoxRows + warp * 4;
+                float4 b_value[4];
 #pragma unroll
-            for (int u = 0; u < kAhead; ++u) {
-                const int kc = (group + u * kWarps) * kGroupRows;
-                if (group + u * kWarps >= kChunkGroups) { break; }
+                for (int r = 0; r < 4; ++r) { b_value[r] = *reinterpret_cast<const float4*>(rows + r * (kStripColumns * 4)); }
+                __syncwarp();
+                if (lane == 0) { mbarrierArrive(&empty[s]); }  // the box is in registers now
+                if (warp == 0 && box >= 1 && issued < boxes) {
+                    const std::uint32_t freed = box - 1;  // its slot takes box freed + kSlots == issued
+                    if (!__all_sync(0xFFFFFFFFU, mbarrierWait(&empty[freed % kSlots], (freed / kSlots) & 1, &abort_flag))) {
+                        abort_flag = 1;
+                        ok         = false;
+                        break;
+                    }
+                    if (lane == 0) { issue_box(issued); }
+                    ++issued;
+                    __syncwarp();
+                }
 #pragma unroll
                 for (int i = 0; i < kRows; ++i) {
-                    // One 128-bit shared load, the same address for the whole warp.
-                    const float4 four      = *reinterpret_cast<const float4*>(&a_chunk[i][kc]);
+                    const float4 four      = *reinterpret_cast<const float4*>(&a_stage[parity][i][kc]);
                     const float a_value[4] = {four.x, four.y, four.z, four.w};
 #pragma unroll
-                    for (int r = 0; r < kGroupRows; ++r) {
-                        acc[i].x = fmaf(a_value[r], b_value[u][r].x, acc[i].x);
-                        acc[i].y = fmaf(a_value[r], b_value[u][r].y, acc[i].y);
-                        acc[i].z = fmaf(a_value[r], b_value[u][r].z, acc[i].z);
-                        acc[i].w = fmaf(a_value[r], b_value[u][r].w, acc[i].w);
+                    for (int r = 0; r < 4; ++r) {
+                        acc[i].x = fmaf(a_value[r], b_value[r].x, acc[i].x);
+                        acc[i].y = fmaf(a_value[r], b_value[r].y, acc[i].y);
+                        acc[i].z = fmaf(a_value[r], b_value[r].z, acc[i].z);
+                        acc[i].w = fmaf(a_value[r], b_value[r].w, acc[i].w);
                     }
                 }
             }
         }
     }
-    __syncthreads();  // the pool changes its role
-
-    // Warps fold into the shared tile one after the other.
-    for (int turn = 0; turn < kWarps; ++turn) {
-        if (warp == turn) {
-#pragma unroll
-            for (int i = 0; i < kRows; ++i) {
-                if (turn == 0) {
-                    tile[i][lane] = acc[i];
-                } else {
-                    float4 sum = tile[i][lane];
-                    sum.x += acc[i].x;
-                    sum.y += acc[i].y;
-                    sum.z += acc[i].z;
-                    sum.w += acc[i].w;
-                    tile[i][lane] = sum;
-                }
+    __syncthreads();  // every box is consumed: the ring changes its role
+    const bool failed = abort_flag != 0;
+    if (failed) {
+        // Copies still in flight must land before this CTA's shared memory goes away.
+        if (warp == 0 && lane == 0) {
+            for (std::uint32_t box = issued > kSlots ? issued - kSlots : 0; box < issued; ++box) {
+                mbarrierWait(&full[box % kSlots], (box / kSlots) & 1, &never_abort);
             }
         }
-        __syncthreads();
+        if (threadIdx.x == 0 && p.status != nullptr) { *p.status = 3; }
     }
-    cluster.sync();
-    if (rank == 0) {
-        for (int item = threadIdx.x; item < kRows * 32; item += kWarps * 32) {
-            const int i                 = item >> 5;
-            const int quad              = item & 31;
-            const std::uint32_t out_col = blockIdx.x * kStripColumns + quad * 4;
+
+    // ---- reduction, in a fixed order throughout.
+    // (1) Every consumer warp parks its sums; then each (row, quad) is summed over
+    //     the warps in warp order.
+    // (2) The strip's 32 quads of columns are shared out among the CTAs of the
+    //     cluster; every CTA sends each of its sums to the owner's `received`
+    //     array (a remote shared-memory store), in the slot of the sender's rank.
+    // (3) After the cluster barrier the owner adds the ranks' contributions in
+    //     rank order, applies alpha and beta and writes D. Nobody touches remote
+    //     shared memory after the barrier, so CTAs may leave independently.
+    if (!failed) {
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) { part[warp][i][lane] = acc[i]; }
+    }
+    __syncthreads();
+    clusterWait();  // second half of the start-up barrier: long complete by now
+    const unsigned quads_per_rank = 32 / ranks;
+    if (!failed) {
+        for (int item = threadIdx.x; item < kRows * 32; item += kThreads) {
+            const int i    = item >> 5;
+            const int quad = item & 31;
+            float4 sum     = part[0][i][quad];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) { sum = add4(sum, part[w][i][quad]); }
+            const unsigned owner = quad / quads_per_rank;
+            float4* remote       = cluster.map_shared_rank(received, owner);
+            remote[(rank * kRows + i) * quads_per_rank + quad % quads_per_rank] = sum;
+        }
+    }
+    clusterArrive();
+    clusterWait();
+    if (abort_flag == 0) {
+        for (int item = threadIdx.x; item < kRows * static_cast<int>(quads_per_rank); item += kThreads) {
+            const int i                 = item / quads_per_rank;
+            const unsigned local_quad   = item % quads_per_rank;
+            const std::uint32_t out_col = strip_col + (rank * quads_per_rank + local_quad) * 4;
             if (i >= slab_rows || out_col >= p.n) { continue; }
-            const std::int64_t out_row = static_cast<std::int64_t>(row0) + i;
-            float4 sum = tile[i][quad];
-            for (unsigned other = 1; other < ranks; ++other) {
-                const float4* remote = cluster.map_shared_rank(&tile[0][0], other);
-                const float4 next    = remote[i * 32 + quad];
-                sum.x += next.x;
-                sum.y += next.y;
-                sum.z += next.z;
-                sum.w += next.w;
+            float4 contribution[kMaxCluster];
+#pragma unroll
+            for (unsigned r = 0; r < kMaxCluster; ++r) {
+                contribution[r] = r < ranks ? received[(r * kRows + i) * quads_per_rank + local_quad] : make_float4(0.0F, 0.0F, 0.0F, 0.0F);
             }
-            const float parts[4] = {sum.x, sum.y, sum.z, sum.w};
+            float4 sum = contribution[0];
+#pragma unroll
+            for (unsigned r = 1; r < kMaxCluster; ++r) {
+                if (r < ranks) { sum = add4(sum, contribution[r]); }
+            }
+            const std::int64_t out_row = static_cast<std::int64_t>(row0) + i;
+            const float parts[4]       = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
+                if (out_col + j >= p.n) { continue; }
                 float value = p.alpha * parts[j];
                 if (p.c != nullptr) {
                     value += p.beta * p.c[out_row * p.c_row_stride + static_cast<std::int64_t>(out_col + j) * p.c_col_stride];
@@ -199,8 +329,11 @@ __global__ void __launch_bounds__(kWarps * 32) skinnyGemm(const SkinnyParams p) 
             }
         }
     }
-    // Nobody's shared memory may go away while the first CTA still reads it.
-    cluster.sync();
+}
+
+template<int kRows>
+cudaError_t allowSharedMemory() {
+    return cudaFuncSetAttribute(skinnyGemm<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(kRows)));
 }
 
 template<int kRows>
@@ -208,7 +341,7 @@ cudaError_t launchRows(const LaunchState& state, const SkinnyParams& p, cudaStre
     cudaLaunchConfig_t config{};
     config.gridDim          = dim3(state.grid_x, state.grid_y, state.grid_z);
     config.blockDim         = dim3(state.block, 1, 1);
-    config.dynamicSmemBytes = 0;
+    config.dynamicSmemBytes = state.smem_bytes;
     config.stream           = stream;
     cudaLaunchAttribute attribute{};
     attribute.id               = cudaLaunchAttributeClusterDimension;
@@ -217,7 +350,7 @@ cudaError_t launchRows(const LaunchState& state, const SkinnyParams& p, cudaStre
     attribute.val.clusterDim.z = 1;
     config.attrs               = &attribute;
     config.numAttrs            = 1;
-    return cudaLaunchKernelEx(&config, skinnyGemm<kRows>, p);
+    return cudaLaunchKernelEx(&config, skinnyGemm<kRows>, state.map_b, p);
 }
 
 }  // namespace
@@ -226,11 +359,9 @@ const char* supportsSkinny(const FtcudaGemmDesc& desc) {
     if (desc.m == 0 || desc.m > 32) { return "more than 32 rows (or none) in A"; }
     if (desc.n == 0 || desc.k == 0) { return "the problem is empty"; }
     if (desc.n >= (1ULL << 31) || desc.k >= (1ULL << 31)) { return "an extent does not fit 31 bits"; }
-    if (desc.n % 4 != 0) { return "n is not a multiple of 4"; }
-    if (desc.b_col_stride != 1 || desc.b_row_stride % 4 != 0 || desc.b_row_stride < static_cast<std::int64_t>(desc.n)) {
-        return "B is not row-major with a 16-byte row pitch";
+    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k)) {
+        return "B is not row-major with a 16-byte aligned base and row pitch";
     }
-    if (reinterpret_cast<std::uintptr_t>(desc.b) % 16 != 0) { return "B is not 16-byte aligned"; }
     return nullptr;
 }
 
@@ -238,28 +369,43 @@ int configureSkinny(LaunchState& state, char* message, std::size_t capacity) {
     const FtcudaGemmDesc& desc = state.desc;
     int sms                    = 0;
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
+    if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
     state.variant         = kVariantGeneric;
     state.grid_x          = static_cast<std::uint32_t>(ceilDiv(desc.n, kStripColumns));
-    state.block           = kWarps * 32;
-    state.smem_bytes      = 0;
+    state.block           = kThreads;
     state.splits          = 1;
     state.workspace_bytes = 0;
-    // Up to eight rows of A per CTA; more rows become slabs along blockIdx.z. The
-    // slabs of a strip run side by side and read the same rows of B, which
-    // therefore come from HBM once and from L2 for the other slabs. Eight rows
-    // keep the accumulators small enough for sixteen loads in flight per warp.
-    state.row_tile = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : 8;
-    state.grid_z   = static_cast<std::uint32_t>(ceilDiv(desc.m, state.row_tile));
-    // CTAs per cluster (= K slices per strip): enough to put two CTAs on every
-    // SM, as long as each CTA keeps at least two groups of K rows per warp.
-    const std::uint64_t groups = ceilDiv(desc.k, kGroupRows);
-    std::uint32_t cluster      = 1;
-    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * state.grid_z * cluster < 2ULL * sms &&
-           groups / (cluster * 2) >= 2ULL * kWarps) {
+    // All rows of A (at most 32) stay in one CTA's registers, so B is read once.
+    state.row_tile   = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : desc.m <= 8 ? 8 : desc.m <= 16 ? 16 : desc.m <= 24 ? 24 : 32;
+    state.grid_z     = static_cast<std::uint32_t>(ceilDiv(desc.m, state.row_tile));
+    state.smem_bytes = smemBytes(static_cast<int>(state.row_tile));
+    // CTAs per cluster (= K slices per strip): as many as still fit the GPU in one
+    // wave, as long as each CTA keeps at least four boxes of K rows.
+    const std::uint64_t resident = static_cast<std::uint64_t>(sms) * ctasPerSm(static_cast<int>(state.row_tile));
+    const std::uint64_t boxes    = ceilDiv(desc.k, kBoxRows);
+    std::uint32_t cluster        = 1;
+    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * state.grid_z * cluster * 2 <= resident &&
+           boxes / (cluster * 2) >= 4) {
         cluster *= 2;
     }
     state.grid_y      = cluster;
-    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(groups, cluster));  // groups per CTA
+    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(boxes, cluster)) * kBoxRows;  // K rows per CTA
+    if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k, static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float),
+                           kStripColumns, kBoxRows, false, message, capacity)) {
+        return 1;
+    }
+    // More than 48 KiB of dynamic shared memory is a per-device opt-in.
+    cudaError_t error = cudaSuccess;
+    switch (state.row_tile) {
+        case 1: error = allowSharedMemory<1>(); break;
+        case 2: error = allowSharedMemory<2>(); break;
+        case 4: error = allowSharedMemory<4>(); break;
+        case 8: error = allowSharedMemory<8>(); break;
+        case 16: error = allowSharedMemory<16>(); break;
+        case 24: error = allowSharedMemory<24>(); break;
+        default: error = allowSharedMemory<32>(); break;
+    }
+    if (error != cudaSuccess) { return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error)); }
     return 0;
 }
 
@@ -280,16 +426,20 @@ cudaError_t launchSkinny(const LaunchState& state, cudaStream_t stream) {
     p.m              = static_cast<std::uint32_t>(desc.m);
     p.n              = static_cast<std::uint32_t>(desc.n);
     p.k              = static_cast<std::uint32_t>(desc.k);
-    p.groups_per_cta = state.k_per_split;
+    p.rows_per_cta   = state.k_per_split;
     p.rows_per_z     = state.row_tile;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
+    p.status         = state.device_status;
     cudaError_t error = cudaSuccess;
     switch (state.row_tile) {
         case 1: error = launchRows<1>(state, p, stream); break;
         case 2: error = launchRows<2>(state, p, stream); break;
         case 4: error = launchRows<4>(state, p, stream); break;
-        default: error = launchRows<8>(state, p, stream); break;
+        case 8: error = launchRows<8>(state, p, stream); break;
+        case 16: error = launchRows<16>(state, p, stream); break;
+        case 24: error = launchRows<24>(state, p, stream); break;
+        default: error = launchRows<32>(state, p, stream); break;
     }
     countLaunches(1);
     return error;

@@ -13,7 +13,9 @@
 //               swizzled boxes. Three K blocks of raw data in flight cover the
 //               L2 latency, independently of the stages below.
 //   warps 4-7   A converters, one thread per row of A: they read their row from
-//               the raw slot, split it and store a_hi / a_lo into TENSOR MEMORY
+//               the raw slot (for an A given contiguous along M -- a transposed
+//               view -- the raw tile is [k][m] and a thread reads its column),
+//               split it and store a_hi / a_lo into TENSOR MEMORY
 //               (tcgen05.st), from where the MMA takes its A operand. A never
 //               occupies MMA-side shared memory or its read bandwidth.
 //   warps 2,3,  B converters, one 32x32 box per warp: transpose-and-split into
@@ -95,6 +97,7 @@ struct TensorParams {
     std::uint32_t splits, k_per_split;
     std::uint32_t chunk_k_blocks;
     std::uint32_t band_m_tiles;  // M tiles walked together, so that concurrent CTAs share B panels in L2
+    std::uint32_t a_m_contiguous;  // A was given contiguous along M (a transposed view): raw tile is [k][m]
     float alpha, beta;
     float* partials;  // non-null: raw sums to partials[split][m][n]
     int* status;
@@ -258,7 +261,11 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) { break; }
                 if (lane == 0) {
                     mbarrierArriveExpectTx(&bars->raw_full[r], kRawSlotBytes);
-                    tmaLoad2d(slot, &map_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
+                    if (p.a_m_contiguous != 0) {
+                        tmaLoad2d(slot, &map_a, &bars->raw_full[r], static_cast<std::int32_t>(w.tile_m), k_coord);
+                    } else {
+                        tmaLoad2d(slot, &map_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
+                    }
                     for (int q = 0; q < kBoxes; ++q) {
                         tmaLoad2d(slot + kRawABytes + q * kBoxBytes, &map_b, &bars->raw_full[r],
                                   static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
@@ -357,9 +364,21 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         float lo[16];
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            const int chunk  = half * 4 + c;
-                            const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
-                            const float values[4] = {raw.x, raw.y, raw.z, raw.w};
+                            const int chunk = half * 4 + c;
+                            float values[4];
+                            if (p.a_m_contiguous != 0) {
+                                // Raw tile is [32 k][128 m], linear: a column per thread,
+                                // consecutive lanes read consecutive words.
+                                const float* column = reinterpret_cast<const float*>(slot) + a_row;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) { values[j] = column[(chunk * 4 + j) * kTileM]; }
+                            } else {
+                                const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
+                                values[0] = raw.x;
+                                values[1] = raw.y;
+                                values[2] = raw.z;
+                                values[3] = raw.w;
+                            }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 std::uint32_t hi_bits, lo_bits;
@@ -533,8 +552,9 @@ const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
         return "an extent does not fit 31 bits";
     }
     if (desc.k < 32) { return "K is shorter than one K block"; }
-    if (!tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m)) {
-        return "A is not row-major with a 16-byte aligned base and row pitch";
+    if (!tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m) &&
+        !tmaEligible(desc.a, desc.a_row_stride, desc.a_col_stride, desc.m, desc.k)) {
+        return "A is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
     }
     if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k)) {
         return "B is not row-major with a 16-byte aligned base and row pitch";
@@ -549,7 +569,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     int sms                    = 0;
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
     if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
-    state.variant              = kVariantTmaAk;
+    state.variant = tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m) ? kVariantTmaAk : kVariantTmaAm;
     const std::uint64_t tiles  = ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
     state.splits               = 1;
     state.k_per_split          = static_cast<std::uint32_t>(ceilDiv(desc.k, kTileK) * kTileK);
@@ -566,11 +586,15 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     state.smem_bytes          = kSmemBytes;
     state.chunk_k_blocks      = chunkKBlocks();
     state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
-    if (!encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
-                           static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float), kTileK, kTileM, true, message,
-                           capacity)) {
-        return 1;
-    }
+    const bool a_encoded =
+        state.variant == kVariantTmaAk
+            ? encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
+                                static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float), kTileK, kTileM, true,
+                                message, capacity)
+            : encodeTensorMap2d(&state.map_a, desc.a, desc.m, desc.k,
+                                static_cast<std::uint64_t>(desc.a_col_stride) * sizeof(float), kTileM, kTileK, false,
+                                message, capacity);
+    if (!a_encoded) { return 1; }
     if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
                            static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), 32, kTileK, true, message,
                            capacity)) {
@@ -602,6 +626,7 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     p.k_per_split    = state.k_per_split;
     p.chunk_k_blocks = state.chunk_k_blocks;
     p.band_m_tiles   = bandMTiles();
+    p.a_m_contiguous = state.variant == kVariantTmaAm ? 1U : 0U;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
     p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;

@@ -1,4 +1,5 @@
-"""PyTorch binding: `gemm(a, b, c=None, alpha=1.0, beta=0.0) -> Tensor`.
+"""PyTorch binding: `gemm(a, b, c=None, alpha=1.0, beta=0.0) -> Tensor`, plus
+`HostGemm` / `gemm_host` for operands in pinned host memory (host_pipeline.py).
 
 Signature, defaults, checks and error type (RuntimeError) are those of the
 reference binding (python/flash_train/torch/csrc/flash_train_torch.cpp:34-75
@@ -30,4 +31,6 @@ except ModuleNotFoundError as exc:
         "the torch binding has not been built: run `python flash-train_b200/build.py`"
     ) from exc
 
-__all__ = ["gemm", "last_message"]
+from .host_pipeline import HostGemm, band_ranges, gemm_host  # noqa: E402
+
+__all__ = ["gemm", "last_message", "HostGemm", "gemm_host", "band_ranges"]

@@ -330,3 +330,45 @@ def test_plan_reuse_many_executions(capi, gpu):
     torch.cuda.synchronize()
     assert capi.launch_count() - before >= 1000
     assert torch.allclose(d.double(), a.double() @ b.double(), rtol=1e-4, atol=1e-2)
+
+
+@pytest.mark.parametrize("kernel", [0, 1, 2, 4])
+def test_transposed_view_of_a(capi, gpu, oracle, kernel):
+    """A given as the transpose of a contiguous k x m buffer: dims (m, k), strides (1, m)."""
+    torch.manual_seed(31)
+    # K is kept short: a strictly sequential FP32 sum over thousands of N(0,1) products is
+    # by itself further from float64 than twice torch's blocked sum.
+    shapes = [(256, 320, 2304), (132, 200, 4128)]
+    if kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK):
+        shapes.append((256, 2304, 384))  # long K: the tensor kernels sum in blocks
+    for m, k, n in shapes:
+        buffer = torch.randn(k, m, device="cuda")
+        a_view = buffer.t()
+        b = torch.randn(k, n, device="cuda")
+        c = torch.randn(m, n, device="cuda")
+        d, reason = platform_gemm(capi, gpu, kernel, a_view, b, c, 0.75, -1.5)
+        if d is None:
+            pytest.skip(f"{capi.KERNEL_NAMES[kernel]} declines: {reason}")
+        check_against_float64(oracle, d, a_view.contiguous(), b, c, 0.75, -1.5, f"{capi.KERNEL_NAMES[kernel]} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 17, 31, 32])
+def test_few_rows_kernel_row_counts_and_ragged_strips(capi, gpu, oracle, m):
+    """Every row-count variant of the few-rows kernel; n off the 128-column strip and, through a
+    view of a wider buffer, off the multiple of four; K off the 32-row box and long enough for
+    several A stages per CTA."""
+    torch.manual_seed(m)
+    for k, n, pitch in ((1000, 200, 200), (4096 + 36, 130, 132), (8192, 4096, 4096), (257, 517, 520)):
+        a = torch.randn(m, k, device="cuda") / 8
+        wide = torch.randn(k, pitch, device="cuda")
+        b = wide[:, :n]
+        c = torch.randn(m, n, device="cuda")
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_SKINNY, a, b, c, 1.5, -0.25)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, b.contiguous(), c, 1.5, -0.25, f"few rows m={m} k={k} n={n}")
+        # Transposed view of A (k x m buffer).
+        a_view = (torch.randn(k, m, device="cuda") / 8).t()
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_SKINNY, a_view, b, None, 1.0, 0.0)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a_view.contiguous(), b.contiguous(), None, 1.0, 0.0,
+                              f"few rows, transposed A, m={m} k={k} n={n}")
