@@ -45,16 +45,25 @@ WORKLOADS = {
     # name: (m, k, n, seed, b_scale, alpha, beta, with_c)
     "gemm_fp32_16384x4096x14336": (16384, 4096, 14336, 3, "rsqrt_k", 1.0, 0.0, False),
     "gemm_fp32_4096x4096x4096_addend": (4096, 4096, 4096, 1, "one", 1.5, 0.5, True),
+    # Same product with B stored as the n x k weight of a Linear layer and passed as its transposed view.
+    "gemm_fp32_16384x4096x14336_bt": (16384, 4096, 14336, 3, "rsqrt_k", 1.0, 0.0, False),
 }
 # Tall-K workload: K sharded over the ranks, partial products summed by an NCCL reduce-scatter.
 KSPLIT_WORKLOAD = "gemm_fp32_2048x262144x2048_ksplit"
 KSPLIT_SHAPE = (2048, 262144, 2048)
+# Few-rows (memory-bound) shapes of the tail sweep, k = n = 4096, entries U(-1, 1): one GPU streams B once.
+FEW_ROWS_WORKLOADS = {"gemm_fp32_1x4096x4096_fewrows": 1, "gemm_fp32_8x4096x4096_fewrows": 8,
+                      "gemm_fp32_17x4096x4096_fewrows": 17}
+FEW_ROWS_COPIES = 4  # distinct B matrices visited in turn: 4 x 64 MiB is twice the 126 MB L2
 DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on one GPU, from the ncu
 # captures summarised under profiles/ (a benchmark run cannot profile itself).
 MEASURED_DRAM_TRAFFIC = {
     ("gemm_fp32_16384x4096x14336", "Fp32Gemm3xTf32", 1): 3210738432 + 925277440,
     ("gemm_fp32_4096x4096x4096_addend", "Fp32Gemm3xTf32", 1): 383589120 + 55749888,
+    ("gemm_fp32_1x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67142912 + 28416,
+    ("gemm_fp32_8x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67260928 + 43520,
+    ("gemm_fp32_17x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67419392 + 17664,
 }
 CPU_SAMPLE_ROWS = 2048  # rows of A per CPU-baseline step
 
@@ -138,20 +147,46 @@ def make_inputs(workload: str, rank: int, world: int, device):
     if b_scale == "rsqrt_k":
         b = b / (k ** 0.5)
     c = torch.randn(m, n, generator=generator)[rank * rows:(rank + 1) * rows].contiguous() if with_c else None
+    if workload.endswith("_bt"):
+        b = b.t().contiguous()  # n x k buffer; the GEMM sees its (k, n) view with strides (1, k)
     if device is not None:
         a, b = a.to(device), b.to(device)
         c = c.to(device) if c is not None else None
+    if workload.endswith("_bt"):
+        b = b.t()
     return a, b, c, alpha, beta
+
+
+def workload_shape(workload: str):
+    if workload in WORKLOADS:
+        return WORKLOADS[workload][:3]
+    if workload == KSPLIT_WORKLOAD:
+        return KSPLIT_SHAPE
+    return FEW_ROWS_WORKLOADS[workload], 4096, 4096
+
+
+def cpu_inputs(workload: str, rows: int):
+    """The first `rows` rows of A (and C), all of B, on the CPU, with the workload's distributions."""
+    import torch
+
+    if workload in WORKLOADS:
+        a, b, c, alpha, beta = make_inputs(workload, 0, 1, None)
+        return a[:rows].contiguous(), b, (c[:rows].contiguous() if c is not None else None), alpha, beta
+    m, k, n = workload_shape(workload)
+    generator = torch.Generator().manual_seed(2)
+    a = torch.rand(min(rows, m), k, generator=generator) * 2 - 1
+    b = torch.rand(k, n, generator=generator) * 2 - 1
+    return a, b, None, 1.0, 0.0
 
 
 def cpu_reference_run(workload: str, steps: int, warmup: int) -> dict:
     """The reference's PyTorch expression on CPU tensors, timed on a row slice."""
     import torch
 
-    m, k, n, _, _, alpha, beta, with_c = WORKLOADS[workload]
-    a, b, c, alpha, beta = make_inputs(workload, 0, 1, None)
-    rows = min(CPU_SAMPLE_ROWS, m)
-    a, c = a[:rows].contiguous(), (c[:rows].contiguous() if c is not None else None)
+    m, k, n = workload_shape(workload)
+    # Tall K: fewer rows keep a step within seconds.
+    rows = min(CPU_SAMPLE_ROWS if k <= 65536 else 256, m)
+    a, b, c, alpha, beta = cpu_inputs(workload, rows)
     threads = torch.get_num_threads()
 
     def step():
@@ -179,7 +214,7 @@ def run_reference_arm(options) -> int:
         return 0
     steps = min(options.steps, 5)
     baseline = cpu_reference_run(options.workload, steps, min(options.warmup, 1))
-    m, k, n, *_ = WORKLOADS[options.workload]
+    m, k, n = workload_shape(options.workload)
     line = {
         "impl": "reference", "metric": "fp32_gemm_tflops", "value": baseline["value"], "unit": "TFLOP/s",
         "n_gpus": options.gpus, "steps": steps, "warmup": min(options.warmup, 1),
@@ -241,6 +276,81 @@ def plan_reuse_overhead(capi, torch, device) -> dict:
     return {"primitive": plan.primitive_name(0), "host_us_per_call": host * 1e3,
             "device_us_per_call": start_event.elapsed_time(end_event),
             "note": "host time of 1000 ftrainPlanExecutePrimitive calls through ctypes (no sync inside), m=n=k=1024"}
+
+
+def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
+    """m in {1, 8, 17}, k = n = 4096: the selected Primitive is the few-rows kernel and the step is
+    HBM-bound (B is read once). Every rank runs the same problem on its own GPU (replicas)."""
+    from flash_train.capi import GemmBinding, null_operand, tensor_operand
+
+    m, k, n = FEW_ROWS_WORKLOADS[options.workload], 4096, 4096
+    generator = torch.Generator(device=device).manual_seed(2)
+    a = torch.rand(m, k, device=device, generator=generator) * 2 - 1
+    copies = [torch.rand(k, n, device=device, generator=generator) * 2 - 1 for _ in range(FEW_ROWS_COPIES)]
+    d = torch.empty(m, n, device=device)
+    binding = GemmBinding()
+    plans = [binding.make_plan(tensor_operand(a), tensor_operand(b), null_operand(m, n), tensor_operand(d)) for b in copies]
+    index = 0 if options.primitive is None else plans[0].index_of(options.primitive)
+    primitive = plans[0].primitive_name(index)
+    size = plans[0].workspace_bytes(index)
+    workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
+    pointer = workspace.data_ptr() if size else 0
+    stream = torch.cuda.current_stream().cuda_stream
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+    def step():  # one step = one GEMM per copy of B
+        for plan in plans:
+            plan.execute(index, pointer, size, stream)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(options.warmup):
+        step()
+    barrier()
+    start_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = capi.launch_count()
+    with ClockSampler(local_rank) as sampler:
+        start_event.record()
+        for _ in range(options.steps):
+            step()
+        end_event.record()
+        barrier()
+        elapsed_ms = start_event.elapsed_time(end_event)
+    launches = capi.launch_count() - launches_before
+    if distributed:
+        slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(slowest.item())
+    if rank == 0:
+        gemms = options.steps * FEW_ROWS_COPIES
+        ms_per_gemm = elapsed_ms / gemms
+        value = world * 2.0 * m * n * k / (ms_per_gemm * 1e-3) / 1e12
+        peaks = measured_peaks()
+        algorithmic = 4 * (k * n + m * k + m * n)
+        achieved = algorithmic / (ms_per_gemm * 1e-3) / 1e9
+        line = {
+            "metric": "fp32_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": options.steps,
+            "warmup": options.warmup, "ms_per_step": elapsed_ms / options.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": options.workload, "m": m, "k": k, "n": n, "primitive": primitive,
+                       "plan": plans[0].primitive_names(), "gemms_per_step": FEW_ROWS_COPIES,
+                       "partition": "replicas only: every GPU runs the same problem",
+                       "l2": f"{FEW_ROWS_COPIES} B matrices of 64 MiB visited in turn (256 MiB > 126 MB L2)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "traffic": MEASURED_DRAM_TRAFFIC.get((options.workload, primitive, 1)),
+                         "algorithmic_bytes": algorithmic, "peak_source": f"{peaks['source']} hbm_gbs (copy)",
+                         "kernel": "skinnyGemm", "us_per_launch": ms_per_gemm * 1e3},
+            "clocks": sampler.summary(), "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+    return 0
 
 
 def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
@@ -322,7 +432,7 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD])
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD] + sorted(FEW_ROWS_WORKLOADS))
     parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
     parser.add_argument("--primitive", default=None,
                         help="run this Primitive of the Plan instead of index 0 (per-primitive tier), e.g. Fp32Gemm")
@@ -354,6 +464,8 @@ def main() -> int:
 
     if options.workload == KSPLIT_WORKLOAD:
         return run_k_split(options, torch, capi, world, rank, local_rank, device)
+    if options.workload in FEW_ROWS_WORKLOADS:
+        return run_few_rows(options, torch, capi, world, rank, local_rank, device)
 
     m, k, n, *_ = WORKLOADS[options.workload]
     if m % world != 0:
@@ -403,7 +515,7 @@ def main() -> int:
 
     # ---- end to end through the public Python call, host buffers in, host buffer out ----
     e2e = None
-    if not options.no_extras:
+    if not options.no_extras and b.is_contiguous():  # HostGemm takes contiguous host matrices
         a_host, b_host = a.cpu().pin_memory(), b.cpu().pin_memory()
         c_host = c.cpu().pin_memory() if c is not None else None
         d_host = torch.empty(rows, n).pin_memory()

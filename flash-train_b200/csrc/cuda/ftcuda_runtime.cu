@@ -121,7 +121,7 @@ bool tmaEligible(const void* base, std::int64_t contiguous_stride, std::int64_t 
 
 bool encodeTensorMap2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t outer,
                        std::uint64_t row_pitch_bytes, std::uint32_t box_inner, std::uint32_t box_outer,
-                       bool swizzle_128b, char* message, std::size_t capacity) {
+                       int swizzle, char* message, std::size_t capacity) {
     const PFN_cuTensorMapEncodeTiled_v12000 encode = tensorMapEncoder();
     if (encode == nullptr) {
         fail(message, capacity, 1, "the CUDA driver does not provide cuTensorMapEncodeTiled");
@@ -133,7 +133,9 @@ bool encodeTensorMap2d(CUtensorMap* map, const void* base, std::uint64_t inner, 
     const cuuint32_t elements[2] = {1, 1};
     const CUresult result        = encode(
         map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elements,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle == kSwizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                               : swizzle == kSwizzle128Atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (result != CUDA_SUCCESS) {
         fail(message, capacity, 1, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(result));

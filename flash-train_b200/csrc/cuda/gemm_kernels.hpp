@@ -19,6 +19,8 @@ enum Variant : int {
     kVariantGeneric  = 0,  // predicated loads, any strides (SIMT only)
     kVariantTmaAk    = 1,  // TMA; A rows contiguous along K (row-major A)
     kVariantTmaAm    = 2,  // TMA; A contiguous along M (transposed view of a K x M buffer)
+    kVariantMaskA    = 15,
+    kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
 };
 
 // What ftcuda_gemm_configure stores inside an FtcudaGemmLaunch.
@@ -55,11 +57,15 @@ bool deviceSmCount(int device, int* sm_count, char* message, std::size_t capacit
 // gave up on a wait. Returns false (with message) on a CUDA error.
 bool deviceStatusWord(int device, int** device_pointer, const volatile int** host_pointer, char* message,
                       std::size_t capacity);
+// Shared-memory swizzle of a tiled copy. kSwizzle128: 16-byte chunks of a 128-byte
+// row XOR-ed with row % 8. kSwizzle128Atom32: 32-byte chunks XOR-ed with row % 4
+// (the layout the tensor cores want for an MN-major operand of 32-bit elements).
+enum TensorMapSwizzle : int { kSwizzleNone = 0, kSwizzle128 = 1, kSwizzle128Atom32 = 2 };
 // Encodes a 2-D FP32 tiled TMA descriptor: `inner` contiguous elements per row,
 // `outer` rows, `row_pitch_bytes` between rows, box = box_inner x box_outer.
 bool encodeTensorMap2d(CUtensorMap* map, const void* base, std::uint64_t inner, std::uint64_t outer,
                        std::uint64_t row_pitch_bytes, std::uint32_t box_inner, std::uint32_t box_outer,
-                       bool swizzle_128b, char* message, std::size_t capacity);
+                       int swizzle, char* message, std::size_t capacity);
 void countLaunches(std::uint64_t launches);
 
 // True when `base`/strides describe a matrix TMA can fetch with `contiguous`

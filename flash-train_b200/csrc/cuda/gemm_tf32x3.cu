@@ -10,7 +10,8 @@
 //   warp 0      TMA producer. Per K block it fetches the raw FP32 operands into
 //               one slot of a 3-deep ring: the 128x32 A tile (rows of 128 bytes,
 //               128-byte swizzle) and the 32x192 B tile as six 32(k) x 32(n)
-//               swizzled boxes. Three K blocks of raw data in flight cover the
+//               swizzled boxes (or one 192(n) x 32(k) box when B is contiguous
+//               along K). Three K blocks of raw data in flight cover the
 //               L2 latency, independently of the stages below.
 //   warps 4-7   A converters, one thread per row of A: they read their row from
 //               the raw slot (for an A given contiguous along M -- a transposed
@@ -18,13 +19,17 @@
 //               split it and store a_hi / a_lo into TENSOR MEMORY
 //               (tcgen05.st), from where the MMA takes its A operand. A never
 //               occupies MMA-side shared memory or its read bandwidth.
-//   warps 2,3,  B converters, one 32x32 box per warp: transpose-and-split into
-//   16-19
-//               K-major B_hi / B_lo shared-memory tiles (128-byte swizzle), the
-//               layout of the B operand of a "TN" GEMM. Lane <-> k makes both
-//               the 128-bit reads and the 32-bit writes bank-conflict free.
+//   warps 2,3,  B converters, 4 KiB of the B tile per warp. The raw tile already has
+//   16-19       the layout the MMA reads: for a row-major B the six boxes (copied
+//               with the 32-byte-base variant of the 128-byte swizzle) are the
+//               swizzle atoms of an MN-major operand (N contiguous), for a B given
+//               contiguous along K (a transposed view, one 32(k) x 192(n) box) it
+//               is a K-major operand. Either way the split is element by element:
+//               128-bit reads and writes at the same offset into B_hi / B_lo,
+//               consecutive lanes at consecutive addresses.
 //   warp 1      MMA issuer (one thread): 4 K-steps x 3 products per K block,
-//               A from tensor memory, B by shared-memory descriptor, into the
+//               A from tensor memory, B by shared-memory descriptor (MN-major or
+//               K-major, see above), into the
 //               "chunk" accumulator (TMEM columns 0-191). A tcgen05.commit per
 //               K block releases the stage (its B tiles and its A columns).
 //   warps 8-15  drain / epilogue. Every `chunk_k_blocks` K blocks the chunk
@@ -98,6 +103,7 @@ struct TensorParams {
     std::uint32_t chunk_k_blocks;
     std::uint32_t band_m_tiles;  // M tiles walked together, so that concurrent CTAs share B panels in L2
     std::uint32_t a_m_contiguous;  // A was given contiguous along M (a transposed view): raw tile is [k][m]
+    std::uint32_t b_k_contiguous;  // B was given contiguous along K (a transposed view): raw tile is [n][k], swizzled
     float alpha, beta;
     float* partials;  // non-null: raw sums to partials[split][m][n]
     int* status;
@@ -266,9 +272,14 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     } else {
                         tmaLoad2d(slot, &map_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
                     }
-                    for (int q = 0; q < kBoxes; ++q) {
-                        tmaLoad2d(slot + kRawABytes + q * kBoxBytes, &map_b, &bars->raw_full[r],
-                                  static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
+                    if (p.b_k_contiguous != 0) {
+                        // One box: 192 rows (n) of 32 K values, already in the MMA's K-major layout.
+                        tmaLoad2d(slot + kRawABytes, &map_b, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_n));
+                    } else {
+                        for (int q = 0; q < kBoxes; ++q) {
+                            tmaLoad2d(slot + kRawABytes + q * kBoxBytes, &map_b, &bars->raw_full[r],
+                                      static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
+                        }
                     }
                 }
                 __syncwarp();
@@ -277,7 +288,10 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!ok) { *abort_flag = 1; }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr std::uint32_t kInstruction = umaInstructionTf32(kTileM, kTileN);
+        // Row-major B stays N-contiguous in shared memory (MN-major operand); a B
+        // given contiguous along K is a K-major operand.
+        const std::uint32_t kInstruction =
+            umaInstructionTf32(kTileM, kTileN) | (p.b_k_contiguous != 0 ? 0U : kUmaBMnMajor);
         std::uint32_t it     = 0;
         std::uint32_t chunks = 0;  // chunks started so far, over all items
         bool ok              = true;
@@ -298,15 +312,20 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tcgen05FenceAfterSync();
                 if (lane == 0) {
                     const std::uint32_t stage = smemAddress(smem + kStageOffset + s * kStageBytes);
-                    const std::uint64_t b_hi  = umaDescriptorK128(stage + kBHiOffset);
-                    const std::uint64_t b_lo  = umaDescriptorK128(stage + kBLoOffset);
+                    const bool k_major        = p.b_k_contiguous != 0;
+                    const std::uint64_t b_hi  = k_major ? umaDescriptorK128(stage + kBHiOffset)
+                                                        : umaDescriptorMn128Base32(stage + kBHiOffset, kBoxBytes, 512);
+                    const std::uint64_t b_lo  = k_major ? umaDescriptorK128(stage + kBLoOffset)
+                                                        : umaDescriptorMn128Base32(stage + kBLoOffset, kBoxBytes, 512);
+                    // Eight k further: 32 bytes within a K-major row, two 512-byte atoms in an MN-major tile.
+                    const std::uint64_t k_step = k_major ? 2 : 64;
                     const std::uint32_t a_hi  = tmem_base + kAColumn + s * 64;
                     const std::uint32_t a_lo  = a_hi + 32;
 #pragma unroll
                     for (int step = 0; step < kTileK / 8; ++step) {
                         // 8 TF32 elements further along K: 8 columns of tensor
-                        // memory for A, 32 bytes = +2 descriptor units for B.
-                        const std::uint64_t advance = static_cast<std::uint64_t>(step * 2);
+                        // memory for A, `k_step` descriptor units (of 16 bytes) for B.
+                        const std::uint64_t advance = static_cast<std::uint64_t>(step) * k_step;
                         const std::uint32_t fresh   = (chunk_start && step == 0) ? 0U : 1U;
                         umaTf32TmemA(tmem_base, a_lo + step * 8, b_hi + advance, kInstruction, fresh);
                         umaTf32TmemA(tmem_base, a_hi + step * 8, b_lo + advance, kInstruction, 1U);
@@ -334,8 +353,6 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool converts_a = warp >= kFirstAConverter && warp < kFirstEpilogue;
         const int box_index   = warp < kFirstAConverter ? warp - 2 : warp - kFirstLateB + 2;  // B box of a B converter
         const int a_row       = 32 * (warp & 3) + lane;   // row of A = TMEM lane (warp % 4 selects the lane quadrant)
-        // Lanes 16-31 take their k rows of a B box in an order shifted by four.
-        const int kk = lane ^ ((lane & 16) >> 2);
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
@@ -392,25 +409,25 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     }
                     tmemStoreWait();
                 } else {
-                    // B: one lane per k. A 128-bit read takes 4 consecutive n at one
-                    // k from the raw box (rows of 128 bytes indexed by k, 16-byte
-                    // chunks XOR-swizzled by k % 8); four 32-bit writes put them
-                    // into rows n of the K-major tile (16-byte chunks XOR-swizzled
-                    // by n % 8).
-                    const unsigned char* box = slot + kRawABytes + box_index * kBoxBytes;
+                    // B arrives in the layout the MMA reads it in -- six 32 (n) x 32 (k)
+                    // boxes of an MN-major operand for a row-major B, 192 rows (n) of a
+                    // K-major operand for a B contiguous along K, both with the
+                    // 128-byte swizzle -- so it is split element by element, same offset
+                    // in the raw tile and in B_hi / B_lo. A warp takes 4 KiB, 128 bits
+                    // per lane and step, consecutive lanes at consecutive addresses.
+                    const int offset          = box_index * kBoxBytes;
+                    const unsigned char* rows = slot + kRawABytes + offset;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
-                        const float4 raw = *reinterpret_cast<const float4*>(box + kk * 128 + ((c ^ (kk & 7)) << 4));
-                        const float values[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int n_row = box_index * 32 + c * 4 + j;
-                            const int dst   = n_row * 128 + (((kk >> 2) ^ (n_row & 7)) << 4) + (kk & 3) * 4;
-                            std::uint32_t hi, lo;
-                            splitTf32(values[j], hi, lo);
-                            *reinterpret_cast<std::uint32_t*>(stage + kBHiOffset + dst) = hi;
-                            *reinterpret_cast<std::uint32_t*>(stage + kBLoOffset + dst) = lo;
-                        }
+                        const int at     = c * 512 + lane * 16;
+                        const float4 raw = *reinterpret_cast<const float4*>(rows + at);
+                        uint4 hi, lo;
+                        splitTf32(raw.x, hi.x, lo.x);
+                        splitTf32(raw.y, hi.y, lo.y);
+                        splitTf32(raw.z, hi.z, lo.z);
+                        splitTf32(raw.w, hi.w, lo.w);
+                        *reinterpret_cast<uint4*>(stage + kBHiOffset + offset + at) = hi;
+                        *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
                     }
                 }
                 __syncwarp();
@@ -556,8 +573,9 @@ const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
         !tmaEligible(desc.a, desc.a_row_stride, desc.a_col_stride, desc.m, desc.k)) {
         return "A is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
     }
-    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k)) {
-        return "B is not row-major with a 16-byte aligned base and row pitch";
+    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k) &&
+        !tmaEligible(desc.b, desc.b_row_stride, desc.b_col_stride, desc.k, desc.n)) {
+        return "B is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
     }
     if (ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN) >= (1ULL << 24)) { return "too many output tiles"; }
     if (split_k && desc.k < 2048) { return "K is too short to split"; }
@@ -570,6 +588,8 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
     if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
     state.variant = tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m) ? kVariantTmaAk : kVariantTmaAm;
+    const bool b_n_contiguous = tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    if (!b_n_contiguous) { state.variant |= kVariantFlagBk; }
     const std::uint64_t tiles  = ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
     state.splits               = 1;
     state.k_per_split          = static_cast<std::uint32_t>(ceilDiv(desc.k, kTileK) * kTileK);
@@ -587,7 +607,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     state.chunk_k_blocks      = chunkKBlocks();
     state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
     const bool a_encoded =
-        state.variant == kVariantTmaAk
+        (state.variant & kVariantMaskA) == kVariantTmaAk
             ? encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
                                 static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float), kTileK, kTileM, true,
                                 message, capacity)
@@ -595,11 +615,15 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
                                 static_cast<std::uint64_t>(desc.a_col_stride) * sizeof(float), kTileM, kTileK, false,
                                 message, capacity);
     if (!a_encoded) { return 1; }
-    if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
-                           static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), 32, kTileK, true, message,
-                           capacity)) {
-        return 1;
-    }
+    // B row-major: six boxes of 32 (n) x 32 (k) per K block; B contiguous along K: one box of 32 (k) x 192 (n).
+    const bool b_encoded =
+        b_n_contiguous ? encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
+                                           static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), 32, kTileK,
+                                           kSwizzle128Atom32, message, capacity)
+                       : encodeTensorMap2d(&state.map_b, desc.b, desc.k, desc.n,
+                                           static_cast<std::uint64_t>(desc.b_col_stride) * sizeof(float), kTileK, kTileN,
+                                           kSwizzle128, message, capacity);
+    if (!b_encoded) { return 1; }
     const cudaError_t error =
         cudaFuncSetAttribute(tensorGemm3xTf32, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (error != cudaSuccess) {
@@ -626,7 +650,8 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     p.k_per_split    = state.k_per_split;
     p.chunk_k_blocks = state.chunk_k_blocks;
     p.band_m_tiles   = bandMTiles();
-    p.a_m_contiguous = state.variant == kVariantTmaAm ? 1U : 0U;
+    p.a_m_contiguous = (state.variant & kVariantMaskA) == kVariantTmaAm ? 1U : 0U;
+    p.b_k_contiguous = (state.variant & kVariantFlagBk) != 0 ? 1U : 0U;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
     p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;

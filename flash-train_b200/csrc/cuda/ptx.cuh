@@ -140,6 +140,30 @@ __device__ __forceinline__ std::uint64_t umaDescriptorK128(std::uint32_t smem_ad
     return descriptor;
 }
 
+// Shared-memory operand descriptor for an MN-major tile (the M or N index is
+// the contiguous one) of 32-bit elements. The only layout the tensor cores take
+// for such an operand is the 128-byte swizzle with a 32-byte base: rows of 128
+// bytes hold 32 consecutive MN elements at one k, their 32-byte quarters XOR-ed
+// with k % 4; four consecutive k form one 512-byte swizzle atom. (A TMA load
+// with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B of a box 32 (MN) x 4j (K) produces j
+// such atoms 512 bytes apart.) `mn_atom_bytes` is the distance between atoms
+// along MN (the next 32 elements; "leading" offset, bits [16,30)),
+// `k_atom_bytes` the distance between atoms along K (the next 4 k; "stride"
+// offset, bits [32,46)). Layout code 1 in bits [61,64).
+__device__ __forceinline__ std::uint64_t umaDescriptorMn128Base32(std::uint32_t smem_address, std::uint32_t mn_atom_bytes,
+                                                                  std::uint32_t k_atom_bytes) {
+    std::uint64_t descriptor = 0;
+    descriptor |= static_cast<std::uint64_t>((smem_address & 0x3FFFF) >> 4);
+    descriptor |= static_cast<std::uint64_t>((mn_atom_bytes >> 4) & 0x3FFF) << 16;
+    descriptor |= static_cast<std::uint64_t>((k_atom_bytes >> 4) & 0x3FFF) << 32;
+    descriptor |= static_cast<std::uint64_t>(1) << 46;
+    descriptor |= static_cast<std::uint64_t>(1) << 61;
+    return descriptor;
+}
+
+// Bit of the instruction descriptor that declares the B operand MN-major.
+constexpr std::uint32_t kUmaBMnMajor = 1u << 16;
+
 // Instruction descriptor for kind::tf32, FP32 accumulation, both operands
 // K-major, dense. Bits: [4,6) D format (1 = F32), [7,10) A format (2 = TF32),
 // [10,13) B format (2 = TF32), 15/16 A/B major (0 = K), [17,23) N>>3,

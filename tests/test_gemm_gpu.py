@@ -372,3 +372,39 @@ def test_few_rows_kernel_row_counts_and_ragged_strips(capi, gpu, oracle, m):
         assert d is not None, reason
         check_against_float64(oracle, d, a_view.contiguous(), b.contiguous(), None, 1.0, 0.0,
                               f"few rows, transposed A, m={m} k={k} n={n}")
+
+
+@pytest.mark.parametrize("kernel", [0, 1, 2, 4])
+@pytest.mark.parametrize("a_transposed", [False, True])
+def test_transposed_view_of_b(capi, gpu, oracle, kernel, a_transposed):
+    """B given as the transpose of a contiguous n x k buffer (the weight of a Linear layer):
+    dims (k, n), strides (1, k); alone and together with a transposed view of A."""
+    torch.manual_seed(37)
+    shapes = [(256, 320, 2304), (132, 200, 4128)]
+    if kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK):
+        shapes.append((384, 2304, 256))
+    for m, k, n in shapes:
+        a = (torch.randn(k, m, device="cuda").t() if a_transposed else torch.randn(m, k, device="cuda"))
+        b_view = torch.randn(n, k, device="cuda").t()
+        c = torch.randn(m, n, device="cuda")
+        d, reason = platform_gemm(capi, gpu, kernel, a, b_view, c, -1.25, 0.5)
+        if d is None:
+            pytest.skip(f"{capi.KERNEL_NAMES[kernel]} declines: {reason}")
+        check_against_float64(oracle, d, a.contiguous(), b_view.contiguous(), c, -1.25, 0.5,
+                              f"{capi.KERNEL_NAMES[kernel]} {m}x{k}x{n} B^T{' A^T' if a_transposed else ''}")
+
+
+def test_training_layouts_select_the_tensor_kernel(capi, gpu, oracle):
+    """The three products of a Linear layer y = x W^T with x: tokens x in, W: out x in.
+    forward  y  = x  @ W^T   (B is a transposed view)
+    dgrad    dx = dy @ W     (plain)
+    wgrad    dW = dy^T @ x   (A is a transposed view)"""
+    tokens, features_in, features_out = 1024, 768, 1536
+    torch.manual_seed(41)
+    x = torch.randn(tokens, features_in, device="cuda")
+    w = torch.randn(features_out, features_in, device="cuda") / features_in ** 0.5
+    dy = torch.randn(tokens, features_out, device="cuda")
+    for label, a, b in (("forward", x, w.t()), ("dgrad", dy, w), ("wgrad", dy.t(), x)):
+        d, names = gpu.gemm(a, b)
+        assert names[0] == "Fp32Gemm3xTf32", f"{label}: {names}"
+        check_against_float64(oracle, d, a.contiguous(), b.contiguous(), None, 1.0, 0.0, f"{label} via {names[0]}")
