@@ -21,6 +21,7 @@ enum Variant : int {
     kVariantTmaAm    = 2,  // TMA; A contiguous along M (transposed view of a K x M buffer)
     kVariantMaskA    = 15,
     kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
+    kVariantFlagPair = 32,  // tensor kernel: CTA pairs on 256-row tiles
 };
 
 // What ftcuda_gemm_configure stores inside an FtcudaGemmLaunch.
@@ -78,6 +79,15 @@ bool tmaEligible(const void* base, std::int64_t contiguous_stride, std::int64_t 
 // supports*: nullptr when the family can run the problem, else the reason.
 // configure*: fills `state` (desc, kernel already set); 0 on success.
 // launch*: enqueues; returns the CUDA error of the launch.
+
+namespace tf32x3 {
+struct TensorParams;
+}
+// CTA-pair form of the tensor kernel (gemm_tf32x3_pair.cu), used by configureTensor / launchTensor.
+bool tensorPairEnabled();  // FTCUDA_TF32_PAIR=1 switches it on
+int configureTensorPair(LaunchState& state, char* message, std::size_t capacity);
+cudaError_t launchTensorPair(const LaunchState& state, const tf32x3::TensorParams& p, std::uint32_t items,
+                             cudaStream_t stream);
 
 const char* supportsSimt(const FtcudaGemmDesc& desc, bool split_k);
 int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t capacity);

@@ -56,13 +56,14 @@
 
 #include "gemm_kernels.hpp"
 #include "ptx.cuh"
+#include "tf32x3_common.cuh"
 
 namespace ftcuda {
 namespace {
 
+using namespace tf32x3;
+
 constexpr int kTileM  = 128;
-constexpr int kTileN  = 192;
-constexpr int kTileK  = 32;
 constexpr int kStages   = 2;  // converted (hi/lo) stages
 constexpr int kRawSlots = 3;  // raw K blocks in flight
 
@@ -92,23 +93,6 @@ constexpr int kHalfColumns     = kTileN / 2;   // columns per epilogue warp
 constexpr int kPieces          = kHalfColumns / 16;
 
 
-struct TensorParams {
-    const float* c;
-    float* d;
-    std::int64_t c_row_stride, c_col_stride;
-    std::int64_t d_row_stride, d_col_stride;
-    std::uint32_t m, n, k;
-    std::uint32_t tiles_m, tiles_n;
-    std::uint32_t splits, k_per_split;
-    std::uint32_t chunk_k_blocks;
-    std::uint32_t band_m_tiles;  // M tiles walked together, so that concurrent CTAs share B panels in L2
-    std::uint32_t a_m_contiguous;  // A was given contiguous along M (a transposed view): raw tile is [k][m]
-    std::uint32_t b_k_contiguous;  // B was given contiguous along K (a transposed view): raw tile is [n][k], swizzled
-    float alpha, beta;
-    float* partials;  // non-null: raw sums to partials[split][m][n]
-    int* status;
-};
-
 struct Barriers {
     std::uint64_t raw_full[kRawSlots];
     std::uint64_t raw_empty[kRawSlots];
@@ -120,97 +104,6 @@ struct Barriers {
     std::uint32_t tmem_base;
     int abort_flag;
 };
-
-struct WorkItem {
-    std::uint32_t tile_m, tile_n;  // element offsets
-    std::uint32_t split;
-    std::uint32_t k_begin, k_blocks;
-};
-
-__device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint32_t item) {
-    const std::uint32_t tiles = p.tiles_m * p.tiles_n;
-    WorkItem w;
-    w.split                   = item / tiles;
-    const std::uint32_t tile  = item - w.split * tiles;
-    const std::uint32_t band  = tile / (p.band_m_tiles * p.tiles_n);
-    const std::uint32_t first = band * p.band_m_tiles;
-    const std::uint32_t rows  = min(p.band_m_tiles, p.tiles_m - first);
-    const std::uint32_t rest  = tile - band * p.band_m_tiles * p.tiles_n;
-    w.tile_m                  = (first + rest % rows) * kTileM;
-    w.tile_n                  = (rest / rows) * kTileN;
-    w.k_begin                 = w.split * p.k_per_split;
-    const std::uint32_t k_end = min(p.k, w.k_begin + p.k_per_split);
-    w.k_blocks                = (k_end - w.k_begin + kTileK - 1) / kTileK;
-    return w;
-}
-
-// Rounds to TF32 (10 explicit mantissa bits), to nearest with ties away from
-// zero -- what cvt.rna.tf32.f32 computes -- with two full-rate integer
-// instructions: the conversion unit has a fraction of the ALU's throughput and
-// the converter warps are on the kernel's critical path. Adding half a TF32 ulp
-// to the sign-magnitude bit pattern and clearing the low 13 bits rounds the
-// magnitude; infinities stay infinities.
-__device__ __forceinline__ std::uint32_t tf32Round(float value) {
-    return (__float_as_uint(value) + 0x1000U) & 0xFFFFE000U;
-}
-
-// value = hi + lo (+ a remainder below 2^-22 |value|), both TF32.
-__device__ __forceinline__ void splitTf32(float value, std::uint32_t& hi, std::uint32_t& lo) {
-    hi = tf32Round(value);
-    lo = tf32Round(value - __uint_as_float(hi));
-}
-
-// Element-wise tail of writeRowSegment for outputs that cannot take 128-bit stores.
-__device__ __noinline__ void writeRowSegmentSlow(float* out, std::int64_t out_row_stride, std::int64_t out_col_stride,
-                                                 const float* c, std::int64_t c_row_stride, std::int64_t c_col_stride,
-                                                 float scale, float beta, std::uint32_t row, std::uint32_t col,
-                                                 std::uint32_t n, const float* sum) {
-    for (std::uint32_t j = 0; j < 16 && col + j < n; ++j) {
-        float value = scale * sum[j];
-        if (c != nullptr) {
-            value += beta * c[static_cast<std::int64_t>(row) * c_row_stride + static_cast<std::int64_t>(col + j) * c_col_stride];
-        }
-        out[static_cast<std::int64_t>(row) * out_row_stride + static_cast<std::int64_t>(col + j) * out_col_stride] = value;
-    }
-}
-
-// Writes one row segment of 16 consecutive columns held by one thread.
-__device__ __forceinline__ void writeRowSegment(const TensorParams& p, const WorkItem& w, std::uint32_t row,
-                                                std::uint32_t col, const float (&sum)[16], bool vector_ok) {
-    if (row >= p.m || col >= p.n) { return; }
-    const bool partial = p.partials != nullptr;
-    float* out         = partial ? p.partials + static_cast<std::uint64_t>(w.split) * p.m * p.n : p.d;
-    const std::int64_t out_row_stride = partial ? p.n : p.d_row_stride;
-    const std::int64_t out_col_stride = partial ? 1 : p.d_col_stride;
-    const bool with_c                 = !partial && p.c != nullptr;
-    const float scale                 = partial ? 1.0F : p.alpha;
-    if (vector_ok) {
-        float* out_row     = out + static_cast<std::int64_t>(row) * out_row_stride + col;
-        const float* c_row = with_c ? p.c + static_cast<std::int64_t>(row) * p.c_row_stride + col : nullptr;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (col + q * 4 >= p.n) { continue; }
-            float4 value = make_float4(scale * sum[q * 4 + 0], scale * sum[q * 4 + 1], scale * sum[q * 4 + 2],
-                                       scale * sum[q * 4 + 3]);
-            if (with_c) {
-                const float4 addend = *reinterpret_cast<const float4*>(c_row + q * 4);
-                value.x += p.beta * addend.x;
-                value.y += p.beta * addend.y;
-                value.z += p.beta * addend.z;
-                value.w += p.beta * addend.w;
-            }
-            *reinterpret_cast<float4*>(out_row + q * 4) = value;
-        }
-        return;
-    }
-    // Any strides, any alignment: handed to an out-of-line routine through a
-    // local copy, so that the common path keeps `sum` in registers.
-    float copy[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { copy[j] = sum[j]; }
-    writeRowSegmentSlow(out, out_row_stride, out_col_stride, with_c ? p.c : nullptr, p.c_row_stride, p.c_col_stride,
-                        scale, p.beta, row, col, p.n, copy);
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -257,7 +150,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item);
+            const WorkItem w = decodeItem(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t use    = it / kRawSlots;
@@ -296,7 +189,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks = 0;  // chunks started so far, over all items
         bool ok              = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item);
+            const WorkItem w = decodeItem(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const bool chunk_start = kb % p.chunk_k_blocks == 0;
                 if (chunk_start) {
@@ -356,7 +249,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item);
+            const WorkItem w = decodeItem(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t s      = it % kStages;
@@ -450,7 +343,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks          = 0;
         bool ok                       = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w               = decodeItem(p, item);
+            const WorkItem w               = decodeItem(p, item, kTileM);
             const std::uint32_t num_chunks = (w.k_blocks + p.chunk_k_blocks - 1) / p.chunk_k_blocks;
             const std::uint32_t row        = w.tile_m + lane_base + lane;
             const bool partial             = p.partials != nullptr;
@@ -598,6 +491,21 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
         state.k_per_split = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, wanted), kTileK) * kTileK);
         state.splits      = static_cast<std::uint32_t>(ceilDiv(desc.k, state.k_per_split));
     }
+    // CTA pairs (gemm_tf32x3_pair.cu) take 256-row tiles, two SMs per tile. Opt-in.
+    const std::uint64_t pair_tiles = ceilDiv(desc.m, 2 * kTileM) * ceilDiv(desc.n, kTileN);
+    const std::uint64_t pairs      = static_cast<std::uint64_t>(sms / 2);
+    const bool use_pairs = tensorPairEnabled() && desc.m > kTileM && pairs >= 1 &&
+                           ceilDiv(pair_tiles * state.splits, pairs) * 9 <= ceilDiv(tiles * state.splits, static_cast<std::uint64_t>(sms)) * 10;
+    if (use_pairs) {
+        state.variant |= kVariantFlagPair;
+        const std::uint64_t pair_items = pair_tiles * state.splits;
+        state.grid_x          = static_cast<std::uint32_t>(2 * (pair_items < pairs ? pair_items : pairs));
+        state.grid_y          = 1;
+        state.grid_z          = 1;
+        state.chunk_k_blocks  = chunkKBlocks();
+        state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
+        return configureTensorPair(state, message, capacity);
+    }
     const std::uint64_t items = tiles * state.splits;
     state.grid_x              = static_cast<std::uint32_t>(items < static_cast<std::uint64_t>(sms) ? items : sms);
     state.grid_y              = 1;
@@ -656,9 +564,16 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     p.beta           = desc.beta;
     p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
     p.status         = state.device_status;
-    const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
-    tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
-    cudaError_t error      = cudaGetLastError();
+    cudaError_t error = cudaSuccess;
+    if ((state.variant & kVariantFlagPair) != 0) {
+        p.tiles_m      = static_cast<std::uint32_t>(ceilDiv(desc.m, 2 * kTileM));
+        p.band_m_tiles = p.band_m_tiles > 1 ? p.band_m_tiles / 2 : 1;
+        error          = launchTensorPair(state, p, p.tiles_m * p.tiles_n * p.splits, stream);
+    } else {
+        const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
+        tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+        error = cudaGetLastError();
+    }
     std::uint64_t launches = 1;
     if (error == cudaSuccess && state.splits > 1) {
         error = launchSplitKReduce(desc, static_cast<const float*>(workspace), state.splits, stream);
