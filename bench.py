@@ -53,7 +53,9 @@ KSPLIT_WORKLOAD = "gemm_fp32_2048x262144x2048_ksplit"
 KSPLIT_SHAPE = (2048, 262144, 2048)
 # Few-rows (memory-bound) shapes of the tail sweep, k = n = 4096, entries U(-1, 1): one GPU streams B once.
 FEW_ROWS_WORKLOADS = {"gemm_fp32_1x4096x4096_fewrows": 1, "gemm_fp32_8x4096x4096_fewrows": 8,
-                      "gemm_fp32_17x4096x4096_fewrows": 17}
+                      "gemm_fp32_17x4096x4096_fewrows": 17,
+                      # B as the transposed view of an n x k weight matrix (x @ W^T)
+                      "gemm_fp32_1x4096x4096_fewrows_bt": 1, "gemm_fp32_8x4096x4096_fewrows_bt": 8}
 FEW_ROWS_COPIES = 4  # distinct B matrices visited in turn: 4 x 64 MiB is twice the 126 MB L2
 DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on one GPU, from the ncu
@@ -278,6 +280,25 @@ def plan_reuse_overhead(capi, torch, device) -> dict:
             "note": "host time of 1000 ftrainPlanExecutePrimitive calls through ctypes (no sync inside), m=n=k=1024"}
 
 
+def torch_gemm_overhead(ft_torch, torch, device) -> dict:
+    """The Python convenience call (Args + Plan per call, output allocated per call), m=n=k=1024."""
+    a = torch.randn(1024, 1024, device=device)
+    b = torch.randn(1024, 1024, device=device)
+    for _ in range(50):
+        ft_torch.gemm(a, b)
+    torch.cuda.synchronize()
+    start_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start_event.record()
+    start = time.perf_counter()
+    for _ in range(1000):
+        ft_torch.gemm(a, b)
+    host = time.perf_counter() - start
+    end_event.record()
+    torch.cuda.synchronize()
+    return {"host_us_per_call": host * 1e3, "device_us_per_call": start_event.elapsed_time(end_event),
+            "note": "1000 calls of flash_train.torch.gemm(a, b), m=n=k=1024, no sync inside"}
+
+
 def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
     """m in {1, 8, 17}, k = n = 4096: the selected Primitive is the few-rows kernel and the step is
     HBM-bound (B is read once). Every rank runs the same problem on its own GPU (replicas)."""
@@ -287,6 +308,8 @@ def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
     generator = torch.Generator(device=device).manual_seed(2)
     a = torch.rand(m, k, device=device, generator=generator) * 2 - 1
     copies = [torch.rand(k, n, device=device, generator=generator) * 2 - 1 for _ in range(FEW_ROWS_COPIES)]
+    if options.workload.endswith("_bt"):
+        copies = [b.t().contiguous().t() for b in copies]  # n x k buffers seen as (k, n) views
     d = torch.empty(m, n, device=device)
     binding = GemmBinding()
     plans = [binding.make_plan(tensor_operand(a), tensor_operand(b), null_operand(m, n), tensor_operand(d)) for b in copies]
@@ -585,7 +608,8 @@ def main() -> int:
     if e2e is not None:
         line["e2e"] = e2e
     if not options.no_extras:
-        line["plan_reuse"] = {"native": plan_reuse_native(local_rank), "python_ctypes": plan_reuse_overhead(capi, torch, device)}
+        line["plan_reuse"] = {"native": plan_reuse_native(local_rank), "python_ctypes": plan_reuse_overhead(capi, torch, device),
+                              "python_torch_gemm": torch_gemm_overhead(ft_torch, torch, device)}
         if world == 1:
             baseline = cpu_reference_run(options.workload, 3, 1)
             line["cpu_baseline"] = {key: baseline[key] for key in ("value", "unit", "cores", "kind", "sample")}

@@ -331,9 +331,212 @@ skinnyGemm(const __grid_constant__ CUtensorMap map_b, const SkinnyParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same problem with B given contiguous along K (dims (k, n), strides
+// (1, pitch): the transposed view of an n x k weight matrix W, as in x @ W^T).
+// Every output column is then the dot product of a row of A with a row of W.
+// A strip is 32 rows of W; a box is 32 rows x 128 K values (16 KiB, rows of 512
+// bytes). Warp w takes rows 4w..4w+3 of every box, a lane takes four K values of
+// each (one conflict-free 128-bit shared load per row), multiplies them with
+// the matching four values of every row of A (128-bit shared loads at
+// consecutive addresses) and keeps rows x 4 scalar sums. At the end the 32
+// lanes' sums are added by a butterfly of shuffles, the CTAs of the cluster (K
+// slices) send theirs to the first CTA through distributed shared memory, and
+// that CTA adds them in rank order and writes D. Ring, producer, A stages (one
+// box = one stage of 128 K values) and bounded waits as above.
+constexpr int kBtStripRows = 32;   // rows of W (= output columns) per strip
+constexpr int kBtBoxK      = 128;  // K values per box
+static_assert(kBtStripRows * kBtBoxK * 4 == kBoxBytes, "both box shapes have the same size");
+static_assert(kBtBoxK == kStageRows, "one box per A stage");
+__host__ __device__ constexpr int receiveBytesBt(int rows) { return kMaxCluster * rows * kBtStripRows * 4; }
+constexpr std::uint32_t smemBytesBt(int rows) {
+    return 127 + ringBytes(rows) + stageBytes(rows) + receiveBytesBt(rows) + 2 * slots(rows) * 8;
+}
+
+template<int kRows>
+__global__ void __launch_bounds__(kThreads, ctasPerSm(kRows))
+skinnyGemmBt(const __grid_constant__ CUtensorMap map_b, const SkinnyParams p) {
+    constexpr int kSlots = slots(kRows);
+    extern __shared__ unsigned char smem_raw[];
+    const std::uint32_t align_offset = (128 - (smemAddress(smem_raw) & 127)) & 127;
+    unsigned char* ring              = smem_raw + align_offset;
+    // [stage parity][row of A][k within the box]
+    float (*a_stage)[kRows][kBtBoxK] = reinterpret_cast<float (*)[kRows][kBtBoxK]>(ring + ringBytes(kRows));
+    // first CTA only: [rank of the sender][row of A][row of W within the strip]
+    float* received      = reinterpret_cast<float*>(ring + ringBytes(kRows) + stageBytes(kRows));
+    std::uint64_t* full  = reinterpret_cast<std::uint64_t*>(ring + ringBytes(kRows) + stageBytes(kRows) + receiveBytesBt(kRows));
+    std::uint64_t* empty = full + kSlots;
+    __shared__ int abort_flag;
+    __shared__ int never_abort;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank       = cluster.block_rank();
+    const unsigned ranks      = cluster.num_blocks();
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const std::uint32_t strip_row = blockIdx.x * kBtStripRows;  // first row of W = first output column
+
+    const int slab_rows = static_cast<int>(min(static_cast<std::uint32_t>(kRows), p.m));
+
+    const std::uint32_t k_begin = min(rank * p.rows_per_cta, p.k);
+    const std::uint32_t k_end   = min(k_begin + p.rows_per_cta, p.k);
+    const std::uint32_t boxes   = (k_end - k_begin + kBtBoxK - 1) / kBtBoxK;
+
+    if (threadIdx.x == 0) {
+        abort_flag  = 0;
+        never_abort = 0;
+        for (int s = 0; s < kSlots; ++s) {
+            mbarrierInit(&full[s], 1);
+            mbarrierInit(&empty[s], kWarps);
+        }
+        fenceBarrierInit();
+        prefetchTensorMap(&map_b);
+    }
+    __syncthreads();
+    clusterArrive();  // "every CTA of the cluster runs", second half before the first remote store
+
+    float acc[kRows][4];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) { acc[i][r] = 0.0F; }
+    }
+
+    std::uint32_t issued = 0;
+    auto issue_box = [&](std::uint32_t box) {
+        const std::uint32_t s = box % kSlots;
+        mbarrierArriveExpectTx(&full[s], kBoxBytes);
+        tmaLoad2d(ring + s * kBoxBytes, &map_b, &full[s], static_cast<std::int32_t>(k_begin + box * kBtBoxK),
+                  static_cast<std::int32_t>(strip_row));
+    };
+    if (warp == 0) {
+        issued = min(boxes, static_cast<std::uint32_t>(kSlots));
+        if (lane == 0) {
+            for (std::uint32_t box = 0; box < issued; ++box) { issue_box(box); }
+        }
+        __syncwarp();
+    }
+    const bool vector_copies = p.a_col_stride == 1 && (p.a_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(p.a) & 15) == 0;
+    auto stage_in = [&](std::uint32_t stage_begin, int parity) {
+        if (vector_copies) {
+            for (int item = threadIdx.x; item < kRows * (kBtBoxK / 4); item += kThreads) {
+                const int i            = item / (kBtBoxK / 4);
+                const int kc           = (item % (kBtBoxK / 4)) * 4;
+                const std::uint32_t kk = stage_begin + kc;
+                const bool valid       = i < slab_rows && kk < k_end;
+                const std::uint32_t bytes = valid ? min(k_end - kk, 4U) * 4U : 0U;
+                copyAsync16(&a_stage[parity][i][kc], valid ? p.a + static_cast<std::int64_t>(i) * p.a_row_stride + kk : p.a, bytes);
+            }
+        } else {
+            const bool k_fastest = p.a_col_stride == 1;
+            for (int item = threadIdx.x; item < kRows * kBtBoxK; item += kThreads) {
+                const int i            = k_fastest ? item / kBtBoxK : item % kRows;
+                const int kc           = k_fastest ? item % kBtBoxK : item / kRows;
+                const std::uint32_t kk = stage_begin + kc;
+                const bool valid       = i < slab_rows && kk < k_end;
+                copyAsync4(&a_stage[parity][i][kc],
+                           valid ? p.a + static_cast<std::int64_t>(i) * p.a_row_stride + static_cast<std::int64_t>(kk) * p.a_col_stride : p.a,
+                           valid ? 4U : 0U);
+            }
+        }
+        copyAsyncCommit();
+    };
+    bool ok = true;
+    if (boxes > 0) { stage_in(k_begin, 0); }
+    for (std::uint32_t box = 0; box < boxes; ++box) {
+        const int parity = static_cast<int>(box & 1);
+        copyAsyncWaitAll();
+        __syncthreads();  // this box's values of A are in place; everybody is done with the other stage
+        if (box + 1 < boxes) { stage_in(k_begin + (box + 1) * kBtBoxK, parity ^ 1); }
+        if (!ok) { continue; }
+        const std::uint32_t s = box % kSlots;
+        ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&full[s], (box / kSlots) & 1, &abort_flag));
+        if (!ok) {
+            abort_flag = 1;
+            continue;
+        }
+        const unsigned char* rows = ring + s * kBoxBytes + (warp * 4) * (kBtBoxK * 4) + lane * 16;
+        float4 b_value[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) { b_value[r] = *reinterpret_cast<const float4*>(rows + r * (kBtBoxK * 4)); }
+        __syncwarp();
+        if (lane == 0) { mbarrierArrive(&empty[s]); }
+        if (warp == 0 && box >= 1 && issued < boxes) {
+            const std::uint32_t freed = box - 1;
+            if (!__all_sync(0xFFFFFFFFU, mbarrierWait(&empty[freed % kSlots], (freed / kSlots) & 1, &abort_flag))) {
+                abort_flag = 1;
+                ok         = false;
+                continue;
+            }
+            if (lane == 0) { issue_box(issued); }
+            ++issued;
+            __syncwarp();
+        }
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) {
+            const float4 a_value = *reinterpret_cast<const float4*>(&a_stage[parity][i][lane * 4]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                float sum = acc[i][r];
+                sum       = fmaf(a_value.x, b_value[r].x, sum);
+                sum       = fmaf(a_value.y, b_value[r].y, sum);
+                sum       = fmaf(a_value.z, b_value[r].z, sum);
+                sum       = fmaf(a_value.w, b_value[r].w, sum);
+                acc[i][r] = sum;
+            }
+        }
+    }
+    __syncthreads();
+    const bool failed = abort_flag != 0;
+    if (failed) {
+        if (warp == 0 && lane == 0) {
+            for (std::uint32_t box = issued > kSlots ? issued - kSlots : 0; box < issued; ++box) {
+                mbarrierWait(&full[box % kSlots], (box / kSlots) & 1, &never_abort);
+            }
+        }
+        if (threadIdx.x == 0 && p.status != nullptr) { *p.status = 3; }
+    }
+
+    // Lanes hold sums over disjoint K values: butterfly over the warp, then value
+    // number v (of rows x 4) is sent by lane v % 32 to the first CTA.
+    clusterWait();
+    float* remote = cluster.map_shared_rank(received, 0);
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            float sum = acc[i][r];
+#pragma unroll
+            for (int offset = 16; offset >= 1; offset >>= 1) { sum += __shfl_xor_sync(0xFFFFFFFFU, sum, offset); }
+            if (!failed && lane == ((i * 4 + r) & 31)) { remote[(rank * kRows + i) * kBtStripRows + warp * 4 + r] = sum; }
+        }
+    }
+    clusterArrive();
+    clusterWait();
+    if (rank == 0 && abort_flag == 0) {
+        for (int item = threadIdx.x; item < kRows * kBtStripRows; item += kThreads) {
+            const int i                 = item / kBtStripRows;
+            const int column            = item % kBtStripRows;
+            const std::uint32_t out_col = strip_row + column;
+            if (i >= slab_rows || out_col >= p.n) { continue; }
+            float sum = received[i * kBtStripRows + column];
+            for (unsigned r = 1; r < ranks; ++r) { sum += received[(r * kRows + i) * kBtStripRows + column]; }
+            float value = p.alpha * sum;
+            if (p.c != nullptr) { value += p.beta * p.c[static_cast<std::int64_t>(i) * p.c_row_stride + static_cast<std::int64_t>(out_col) * p.c_col_stride]; }
+            p.d[static_cast<std::int64_t>(i) * p.d_row_stride + static_cast<std::int64_t>(out_col) * p.d_col_stride] = value;
+        }
+    }
+}
+
 template<int kRows>
 cudaError_t allowSharedMemory() {
     return cudaFuncSetAttribute(skinnyGemm<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(kRows)));
+}
+
+template<int kRows>
+cudaError_t allowSharedMemoryBt() {
+    return cudaFuncSetAttribute(skinnyGemmBt<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytesBt(kRows)));
 }
 
 template<int kRows>
@@ -350,6 +553,7 @@ cudaError_t launchRows(const LaunchState& state, const SkinnyParams& p, cudaStre
     attribute.val.clusterDim.z = 1;
     config.attrs               = &attribute;
     config.numAttrs            = 1;
+    if ((state.variant & kVariantFlagBk) != 0) { return cudaLaunchKernelEx(&config, skinnyGemmBt<kRows>, state.map_b, p); }
     return cudaLaunchKernelEx(&config, skinnyGemm<kRows>, state.map_b, p);
 }
 
@@ -359,8 +563,9 @@ const char* supportsSkinny(const FtcudaGemmDesc& desc) {
     if (desc.m == 0 || desc.m > 32) { return "more than 32 rows (or none) in A"; }
     if (desc.n == 0 || desc.k == 0) { return "the problem is empty"; }
     if (desc.n >= (1ULL << 31) || desc.k >= (1ULL << 31)) { return "an extent does not fit 31 bits"; }
-    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k)) {
-        return "B is not row-major with a 16-byte aligned base and row pitch";
+    if (!tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k) &&
+        !tmaEligible(desc.b, desc.b_row_stride, desc.b_col_stride, desc.k, desc.n)) {
+        return "B is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
     }
     return nullptr;
 }
@@ -370,40 +575,45 @@ int configureSkinny(LaunchState& state, char* message, std::size_t capacity) {
     int sms                    = 0;
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
     if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
-    state.variant         = kVariantGeneric;
-    state.grid_x          = static_cast<std::uint32_t>(ceilDiv(desc.n, kStripColumns));
+    const bool b_k_contiguous = !tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    state.variant         = b_k_contiguous ? kVariantFlagBk : kVariantGeneric;
+    const std::uint32_t strip = b_k_contiguous ? kBtStripRows : kStripColumns;  // output columns per strip
+    const std::uint32_t box_k = b_k_contiguous ? kBtBoxK : kBoxRows;            // K values per box
+    state.grid_x          = static_cast<std::uint32_t>(ceilDiv(desc.n, strip));
     state.block           = kThreads;
     state.splits          = 1;
     state.workspace_bytes = 0;
     // All rows of A (at most 32) stay in one CTA's registers, so B is read once.
     state.row_tile   = desc.m <= 1 ? 1 : desc.m <= 2 ? 2 : desc.m <= 4 ? 4 : desc.m <= 8 ? 8 : desc.m <= 16 ? 16 : desc.m <= 24 ? 24 : 32;
-    state.grid_z     = static_cast<std::uint32_t>(ceilDiv(desc.m, state.row_tile));
-    state.smem_bytes = smemBytes(static_cast<int>(state.row_tile));
+    state.grid_z     = 1;
+    const int rows   = static_cast<int>(state.row_tile);
+    state.smem_bytes = b_k_contiguous ? smemBytesBt(rows) : smemBytes(rows);
     // CTAs per cluster (= K slices per strip): as many as still fit the GPU in one
-    // wave, as long as each CTA keeps at least four boxes of K rows.
-    const std::uint64_t resident = static_cast<std::uint64_t>(sms) * ctasPerSm(static_cast<int>(state.row_tile));
-    const std::uint64_t boxes    = ceilDiv(desc.k, kBoxRows);
+    // wave, as long as each CTA keeps at least four boxes.
+    const std::uint64_t resident = static_cast<std::uint64_t>(sms) * ctasPerSm(rows);
+    const std::uint64_t boxes    = ceilDiv(desc.k, box_k);
     std::uint32_t cluster        = 1;
-    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * state.grid_z * cluster * 2 <= resident &&
-           boxes / (cluster * 2) >= 4) {
+    while (cluster < kMaxCluster && static_cast<std::uint64_t>(state.grid_x) * cluster * 2 <= resident && boxes / (cluster * 2) >= 4) {
         cluster *= 2;
     }
     state.grid_y      = cluster;
-    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(boxes, cluster)) * kBoxRows;  // K rows per CTA
-    if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k, static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float),
-                           kStripColumns, kBoxRows, false, message, capacity)) {
-        return 1;
-    }
+    state.k_per_split = static_cast<std::uint32_t>(ceilDiv(boxes, cluster)) * box_k;  // K values per CTA
+    const bool encoded =
+        b_k_contiguous ? encodeTensorMap2d(&state.map_b, desc.b, desc.k, desc.n, static_cast<std::uint64_t>(desc.b_col_stride) * sizeof(float),
+                                           kBtBoxK, kBtStripRows, kSwizzleNone, message, capacity)
+                       : encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k, static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float),
+                                           kStripColumns, kBoxRows, kSwizzleNone, message, capacity);
+    if (!encoded) { return 1; }
     // More than 48 KiB of dynamic shared memory is a per-device opt-in.
     cudaError_t error = cudaSuccess;
     switch (state.row_tile) {
-        case 1: error = allowSharedMemory<1>(); break;
-        case 2: error = allowSharedMemory<2>(); break;
-        case 4: error = allowSharedMemory<4>(); break;
-        case 8: error = allowSharedMemory<8>(); break;
-        case 16: error = allowSharedMemory<16>(); break;
-        case 24: error = allowSharedMemory<24>(); break;
-        default: error = allowSharedMemory<32>(); break;
+        case 1: error = b_k_contiguous ? allowSharedMemoryBt<1>() : allowSharedMemory<1>(); break;
+        case 2: error = b_k_contiguous ? allowSharedMemoryBt<2>() : allowSharedMemory<2>(); break;
+        case 4: error = b_k_contiguous ? allowSharedMemoryBt<4>() : allowSharedMemory<4>(); break;
+        case 8: error = b_k_contiguous ? allowSharedMemoryBt<8>() : allowSharedMemory<8>(); break;
+        case 16: error = b_k_contiguous ? allowSharedMemoryBt<16>() : allowSharedMemory<16>(); break;
+        case 24: error = b_k_contiguous ? allowSharedMemoryBt<24>() : allowSharedMemory<24>(); break;
+        default: error = b_k_contiguous ? allowSharedMemoryBt<32>() : allowSharedMemory<32>(); break;
     }
     if (error != cudaSuccess) { return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error)); }
     return 0;

@@ -434,3 +434,30 @@ def test_cta_pair_form_of_the_tensor_kernel(capi, gpu, oracle, kernel, monkeypat
                               f"pair form {capi.KERNEL_NAMES[kernel]} {m}x{k}x{n}")
         # Both forms split and sum in the same order within a tile row: identical bits.
         assert torch.equal(paired, single), f"pair and single forms differ for {m}x{k}x{n}"
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 17, 24, 32])
+def test_few_rows_kernel_with_b_contiguous_along_k(capi, gpu, oracle, m):
+    """x @ W^T for few rows of x: B is the transposed view of an n x k weight matrix (dims (k, n),
+    strides (1, pitch)). n off the 32-row strip, K off the 128-value box, pitch wider than K, A plain
+    and as a transposed view."""
+    torch.manual_seed(100 + m)
+    for k, n, pitch in ((1000, 200, 1000), (4096 + 36, 130, 4136), (8192, 4096, 8192), (260, 517, 264)):
+        a = torch.randn(m, k, device="cuda") / 8
+        wide = torch.randn(n, pitch, device="cuda")
+        b = wide[:, :k].t()
+        c = torch.randn(m, n, device="cuda")
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_SKINNY, a, b, c, 1.5, -0.25)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, b.contiguous(), c, 1.5, -0.25, f"few rows, W^T, m={m} k={k} n={n}")
+        a_view = (torch.randn(k, m, device="cuda") / 8).t()
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_SKINNY, a_view, b, None, 1.0, 0.0)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a_view.contiguous(), b.contiguous(), None, 1.0, 0.0,
+                              f"few rows, W^T, transposed A, m={m} k={k} n={n}")
+    # Through the Plan: the Finder's first choice for this layout is the few-rows kernel.
+    x = torch.randn(m, 2048, device="cuda")
+    w = torch.randn(1024, 2048, device="cuda")
+    d, names = gpu.gemm(x, w.t())
+    assert names[0] == "Fp32GemmSkinny", names
+    check_against_float64(oracle, d, x, w.t().contiguous(), None, 1.0, 0.0, f"x @ W^T via {names[0]}")
