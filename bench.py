@@ -299,6 +299,54 @@ def torch_gemm_overhead(ft_torch, torch, device) -> dict:
             "note": "1000 calls of flash_train.torch.gemm(a, b), m=n=k=1024, no sync inside"}
 
 
+SWEEP_WORKLOAD = "finder_sweep"
+SWEEP_SHAPES = [(m, k, n) for (k, n) in ((4096, 4096), (1024, 1024), (256, 4096), (16384, 1024), (65536, 512))
+                for m in (1, 8, 17, 32, 33, 64, 128, 256, 1024, 4097)]
+
+
+def run_finder_sweep(options, torch, capi, rank, device) -> int:
+    """Every kernel family that accepts a shape is timed through the platform ABI and compared with the
+    Finder's first choice for it: `regret` = time of the choice / time of the fastest family."""
+    from flash_train.capi import GemmBinding, null_operand, tensor_operand
+
+    if rank != 0:
+        return 0
+    stream = torch.cuda.current_stream().cuda_stream
+    binding = GemmBinding()
+    rows = []
+    for m, k, n in SWEEP_SHAPES:
+        generator = torch.Generator(device=device).manual_seed(m + k + n)
+        a = torch.rand(m, k, device=device, generator=generator) * 2 - 1
+        b = torch.rand(k, n, device=device, generator=generator) * 2 - 1
+        d = torch.empty(m, n, device=device)
+        names = binding.make_plan(tensor_operand(a), tensor_operand(b), null_operand(m, n), tensor_operand(d)).primitive_names()
+        operand = lambda t: (t.data_ptr(), tuple(t.shape), None)  # noqa: E731
+        desc = capi.make_desc(operand(a), operand(b), (0, (m, n), None), operand(d), 1.0, 0.0, device.index or 0)
+        times = {}
+        for kernel, name in capi.KERNEL_NAMES.items():
+            if capi.platform_supports(kernel, desc) is not None:
+                continue
+            launch = capi.PlatformGemm(kernel, desc)
+            workspace = torch.empty(max(launch.workspace_bytes, 1), dtype=torch.uint8, device=device)
+            repeats = 3 if 2.0 * m * n * k > 5e10 else 10
+            for _ in range(2):
+                launch.run(workspace.data_ptr(), launch.workspace_bytes, stream)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(repeats):
+                launch.run(workspace.data_ptr(), launch.workspace_bytes, stream)
+            end.record()
+            torch.cuda.synchronize()
+            times[name] = start.elapsed_time(end) / repeats * 1e3
+        best = min(times, key=times.get)
+        rows.append({"m": m, "k": k, "n": n, "choice": names[0], "best": best, "regret": times[names[0]] / times[best],
+                     "us": {name: round(value, 2) for name, value in times.items()}})
+    worst = max(rows, key=lambda row: row["regret"])
+    print(json.dumps({"metric": "finder_regret", "value": worst["regret"], "unit": "x", "n_gpus": 1, "higher_is_better": False,
+                      "config": {"workload": SWEEP_WORKLOAD, "shapes": len(rows)}, "worst": worst, "rows": rows}), flush=True)
+    return 0
+
+
 def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
     """m in {1, 8, 17}, k = n = 4096: the selected Primitive is the few-rows kernel and the step is
     HBM-bound (B is read once). Every rank runs the same problem on its own GPU (replicas)."""
@@ -455,7 +503,7 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD] + sorted(FEW_ROWS_WORKLOADS))
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD, SWEEP_WORKLOAD] + sorted(FEW_ROWS_WORKLOADS))
     parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
     parser.add_argument("--primitive", default=None,
                         help="run this Primitive of the Plan instead of index 0 (per-primitive tier), e.g. Fp32Gemm")
@@ -489,6 +537,8 @@ def main() -> int:
         return run_k_split(options, torch, capi, world, rank, local_rank, device)
     if options.workload in FEW_ROWS_WORKLOADS:
         return run_few_rows(options, torch, capi, world, rank, local_rank, device)
+    if options.workload == SWEEP_WORKLOAD:
+        return run_finder_sweep(options, torch, capi, rank, device)
 
     m, k, n, *_ = WORKLOADS[options.workload]
     if m % world != 0:

@@ -10,16 +10,24 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 
 }  // namespace
 
-// Regime map on B200 (148 SMs; the count is queried, not assumed):
+// Regime map on B200 (148 SMs; the count is queried, not assumed). The
+// thresholds come from timing every kernel family on a grid of shapes
+// (bench.py --workload finder_sweep) and keeping the Finder's first choice
+// within about 1.4x of the fastest family everywhere on it:
 //   * very few rows of A (m <= 32): B is streamed exactly once, the problem is
-//     HBM-bound -> the skinny kernel first.
-//   * enough rows/columns to fill 128x192 tensor-core tiles: 3xTF32 on tcgen05.
-//     If the last wave of those tiles would leave more than a tenth of the SMs
-//     idle while K is long enough to cut, the split-K variant (workspace
-//     needed) goes first so that K slices even out the waves; the unsplit
-//     kernels follow for callers without workspace.
+//     HBM-bound -> the few-rows kernel first -- unless B is so narrow that its
+//     strips (128 columns, or 32 rows of a B given contiguous along K) times
+//     the 8 K slices of a cluster leave most SMs without a CTA; then, with K
+//     long enough to cut, the tensor-core split-K kernel goes first.
+//   * from 33 rows on, with at least 128 columns: 3xTF32 on tcgen05 (its
+//     128-row tile beats the SIMT kernel even when only a quarter full). If
+//     the 128x192 tiles fill less than 90 % of the SMs' waves and K >= 2048,
+//     the split-K variant (workspace needed) goes first so that K slices even
+//     out the waves; the unsplit kernels follow for callers without workspace.
+//     Under 128 rows with a medium K (512 ... 2047) and few tiles, the exact
+//     split-K SIMT kernel is the fastest.
 //   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
-//     leave most SMs idle and K is long.
+//     leave most SMs idle and K >= 512.
 // Every list ends with "Fp32Gemm", which needs no workspace and accepts every
 // layout, so a caller walking the Plan by workspace budget always finds a
 // runnable index.
@@ -36,18 +44,25 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     const char* simt_split   = cudaGemmName(FTCUDA_GEMM_SIMT_SPLITK);
 
     if (shape.m * shape.n == 0) { return {simt}; }
-    if (shape.m <= 32 && shape.k >= 256) { return {skinny, simt_split, simt}; }
+    if (shape.m <= 32 && shape.k >= 256) {
+        const bool b_along_k           = problem.getLayout(GemmPort::kB).row_stride == 1 && shape.n > 1;
+        const std::uint64_t strip      = b_along_k ? 32 : 128;
+        const std::uint64_t few_ctas   = ceilDiv(shape.n, strip) * 8;  // CTAs the few-rows kernel can start
+        const bool narrow              = few_ctas * 4 <= sm_count || (few_ctas * 2 <= sm_count && shape.m > 8);
+        if (narrow && shape.k >= 2048) { return {tensor_split, skinny, simt_split, simt}; }
+        return {skinny, simt_split, simt};
+    }
 
-    const bool fills_tensor_tiles = shape.m >= 128 && shape.n >= 128 && shape.k >= 256;
-    if (fills_tensor_tiles) {
+    const std::uint64_t simt_tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 128);
+    if (shape.m >= 33 && shape.n >= 128 && shape.k >= 256) {
         const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 192);
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
-        const bool ragged         = tiles * 10 < waves * sm_count * 9;  // last wave under 90 % full overall
-        if (ragged && shape.k >= 8192) { return {tensor_split, tensor, simt_split, simt}; }
+        const bool ragged         = tiles * 10 < waves * sm_count * 9;  // the waves are under 90 % full overall
+        if (ragged && shape.k >= 2048) { return {tensor_split, tensor, simt_split, simt}; }
+        if (shape.m < 128 && shape.k >= 512 && simt_tiles * 2 <= sm_count) { return {simt_split, tensor, simt}; }
         return {tensor, simt};
     }
-    const std::uint64_t simt_tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 128);
-    if (simt_tiles * 2 <= sm_count && shape.k >= 2048) { return {simt_split, simt}; }
+    if (simt_tiles * 2 <= sm_count && shape.k >= 512) { return {simt_split, simt}; }
     return {simt};
 }
 

@@ -239,7 +239,20 @@ TEST(finder_regime_map) {
     using Names = std::vector<std::string>;
     CHECK(first(1, 4096, 4096) == (Names{"Fp32GemmSkinny", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(17, 4096, 4096).front() == "Fp32GemmSkinny");
-    CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    // 2 x 22 tiles on 148 SMs and K long enough to cut: K slices first.
+    CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
+    CHECK(first(4097, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    // From 33 rows on the tensor kernel's 128-row tile wins over the SIMT kernel.
+    CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(64, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    CHECK(first(64, 1024, 1024) == (Names{"Fp32GemmSplitK", "Fp32Gemm3xTf32", "Fp32Gemm"}));
+    // Few rows but a narrow B: too few strips for the few-rows kernel.
+    CHECK(first(17, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(17, 16384, 1024).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(8, 16384, 1024).front() == "Fp32GemmSkinny");
+    CHECK(first(32, 4096, 2048).front() == "Fp32GemmSkinny");
+    CHECK(first(64, 1024, 64) == (Names{"Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(16384, 4096, 14336) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(2048, 262144, 2048) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(128, 64, 96) == (Names{"Fp32Gemm"}));
