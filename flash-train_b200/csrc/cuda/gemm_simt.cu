@@ -66,7 +66,7 @@ __device__ __forceinline__ void storeElement(const SimtParams& p, std::uint32_t 
 
 // kAContiguousK: the A tile is [128 rows][32 k] with 128-byte rows, swizzled;
 // otherwise it is [32 k][128 rows], linear (A was given contiguous along M).
-template<bool kAContiguousK>
+template<bool kAContiguousK, bool kBContiguousK>
 __global__ void __launch_bounds__(kThreads, 2)
 simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const SimtParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -108,7 +108,11 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         } else {
             tmaLoad2d(stage, &map_a, &full[s], static_cast<std::int32_t>(tile_m), k_coord);
         }
-        tmaLoad2d(stage + kTileBytes, &map_b, &full[s], static_cast<std::int32_t>(tile_n), k_coord);
+        if (kBContiguousK) {
+            tmaLoad2d(stage + kTileBytes, &map_b, &full[s], k_coord, static_cast<std::int32_t>(tile_n));
+        } else {
+            tmaLoad2d(stage + kTileBytes, &map_b, &full[s], static_cast<std::int32_t>(tile_n), k_coord);
+        }
     };
     if (tid == 0) {
         for (int block = 0; block < kStages - 1 && block < k_blocks; ++block) { issue(block); }
@@ -168,16 +172,40 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     a_frag[7][kk] = hi.w;
                 }
             }
+            if (kBContiguousK) {
+                // B tile is [128 n][32 k], rows of 128 bytes with the 128-byte swizzle.
+                // A thread owns columns j * 16 + tx: the 8 lanes of a quarter-warp read
+                // 8 consecutive rows, i.e. 8 different 16-byte chunk positions.
+                float b_frag[8][4];
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const unsigned char* b_row = b_tile + (k4 * 4 + kk) * (kTileN * 4);
-                const float4 b0            = *reinterpret_cast<const float4*>(b_row + tx * 16);
-                const float4 b1            = *reinterpret_cast<const float4*>(b_row + 256 + tx * 16);
-                const float b_frag[8]      = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                for (int j = 0; j < 8; ++j) {
+                    const int column   = j * 16 + tx;
+                    const float4 value = *reinterpret_cast<const float4*>(b_tile + column * 128 + ((k4 ^ (column & 7)) << 4));
+                    b_frag[j][0] = value.x;
+                    b_frag[j][1] = value.y;
+                    b_frag[j][2] = value.z;
+                    b_frag[j][3] = value.w;
+                }
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) { acc[i][j] = fmaf(a_frag[i][kk], b_frag[j], acc[i][j]); }
+                    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { acc[i][j] = fmaf(a_frag[i][kk], b_frag[j][kk], acc[i][j]); }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const unsigned char* b_row = b_tile + (k4 * 4 + kk) * (kTileN * 4);
+                    const float4 b0            = *reinterpret_cast<const float4*>(b_row + tx * 16);
+                    const float4 b1            = *reinterpret_cast<const float4*>(b_row + 256 + tx * 16);
+                    const float b_frag[8]      = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { acc[i][j] = fmaf(a_frag[i][kk], b_frag[j], acc[i][j]); }
+                    }
                 }
             }
         }
@@ -193,6 +221,17 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 mbarrierWait(&full[s], 0, &never);
                 mbarrierWait(&full[s], 1, &never);
             }
+        }
+        return;
+    }
+
+    if (kBContiguousK) {
+        // Columns j * 16 + tx: for one (i, j) the 16 lanes of a half-warp write 16
+        // consecutive columns of one row.
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { storeElement(p, tile_m + ty * 8 + i, tile_n + j * 16 + tx, acc[i][j]); }
         }
         return;
     }
@@ -372,12 +411,14 @@ int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t c
 
     // TMA path: both operands describable and at least one full-size tile of
     // work; otherwise the generic kernel.
-    const bool b_ok  = tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    const bool b_n   = tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    const bool b_k   = !b_n && tmaEligible(desc.b, desc.b_row_stride, desc.b_col_stride, desc.k, desc.n);
+    const bool b_ok  = b_n || b_k;
     const bool a_k   = tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m);
     const bool a_m   = tmaEligible(desc.a, desc.a_row_stride, desc.a_col_stride, desc.m, desc.k);
     const bool large = desc.m >= 96 && desc.n >= 96 && desc.k >= 32;
     state.variant    = kVariantGeneric;
-    if (b_ok && large && (a_k || a_m)) { state.variant = a_k ? kVariantTmaAk : kVariantTmaAm; }
+    if (b_ok && large && (a_k || a_m)) { state.variant = (a_k ? kVariantTmaAk : kVariantTmaAm) | (b_k ? kVariantFlagBk : 0); }
 
     const std::uint32_t tile_m = state.variant == kVariantGeneric ? kGenericTile : kTileM;
     const std::uint32_t tile_n = state.variant == kVariantGeneric ? kGenericTile : kTileN;
@@ -405,21 +446,24 @@ int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t c
 
     if (state.variant != kVariantGeneric) {
         const std::uint64_t a_pitch =
-            static_cast<std::uint64_t>(state.variant == kVariantTmaAk ? desc.a_row_stride : desc.a_col_stride) * sizeof(float);
+            static_cast<std::uint64_t>((state.variant & kVariantMaskA) == kVariantTmaAk ? desc.a_row_stride : desc.a_col_stride) * sizeof(float);
         const bool a_encoded =
-            state.variant == kVariantTmaAk
+            (state.variant & kVariantMaskA) == kVariantTmaAk
                 ? encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m, a_pitch, kTileK, kTileM, true, message, capacity)
                 : encodeTensorMap2d(&state.map_a, desc.a, desc.m, desc.k, a_pitch, kTileM, kTileK, false, message, capacity);
         if (!a_encoded) { return 1; }
-        if (!encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k,
-                               static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), kTileN, kTileK, false,
-                               message, capacity)) {
-            return 1;
-        }
+        const bool b_encoded =
+            b_k ? encodeTensorMap2d(&state.map_b, desc.b, desc.k, desc.n, static_cast<std::uint64_t>(desc.b_col_stride) * sizeof(float),
+                                    kTileK, kTileN, kSwizzle128, message, capacity)
+                : encodeTensorMap2d(&state.map_b, desc.b, desc.n, desc.k, static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float),
+                                    kTileN, kTileK, kSwizzleNone, message, capacity);
+        if (!b_encoded) { return 1; }
         // Opting in to 97 KiB of dynamic shared memory is a per-device setting.
-        cudaError_t error = cudaFuncSetAttribute(simtGemmTma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (error == cudaSuccess) {
-            error = cudaFuncSetAttribute(simtGemmTma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t error = cudaSuccess;
+        const void* kernels[4] = {reinterpret_cast<const void*>(simtGemmTma<true, false>), reinterpret_cast<const void*>(simtGemmTma<false, false>),
+                                  reinterpret_cast<const void*>(simtGemmTma<true, true>), reinterpret_cast<const void*>(simtGemmTma<false, true>)};
+        for (const void* kernel : kernels) {
+            if (error == cudaSuccess) { error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes); }
         }
         if (error != cudaSuccess) {
             return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error));
@@ -454,10 +498,18 @@ cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t s
         g.b_col_stride = state.desc.b_col_stride;
         g.out          = out;
         simtGemmGeneric<<<grid, state.block, 0, stream>>>(g);
-    } else if (state.variant == kVariantTmaAk) {
-        simtGemmTma<true><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
     } else {
-        simtGemmTma<false><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+        const bool a_k = (state.variant & kVariantMaskA) == kVariantTmaAk;
+        const bool b_k = (state.variant & kVariantFlagBk) != 0;
+        if (a_k && !b_k) {
+            simtGemmTma<true, false><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+        } else if (!a_k && !b_k) {
+            simtGemmTma<false, false><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+        } else if (a_k) {
+            simtGemmTma<true, true><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+        } else {
+            simtGemmTma<false, true><<<grid, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, out);
+        }
     }
     cudaError_t error = cudaGetLastError();
     std::uint64_t launches = 1;

@@ -48,7 +48,10 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const bool b_along_k           = problem.getLayout(GemmPort::kB).row_stride == 1 && shape.n > 1;
         const std::uint64_t strip      = b_along_k ? 32 : 128;
         const std::uint64_t few_ctas   = ceilDiv(shape.n, strip) * 8;  // CTAs the few-rows kernel can start
-        const bool narrow              = few_ctas * 4 <= sm_count || (few_ctas * 2 <= sm_count && shape.m > 8);
+        // The more rows, the more arithmetic per CTA (from 17 rows on the kernel is
+        // bound by the FP32 pipe and runs one CTA per SM), the more CTAs it needs.
+        const bool narrow = few_ctas * 4 <= sm_count || (few_ctas * 2 <= sm_count && shape.m > 8) ||
+                            (few_ctas <= sm_count && shape.m > 16);
         if (narrow && shape.k >= 2048) { return {tensor_split, skinny, simt_split, simt}; }
         return {skinny, simt_split, simt};
     }

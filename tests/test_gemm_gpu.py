@@ -245,7 +245,7 @@ def test_selection_cache_and_workspace_walk(capi, gpu):
         assert torch.allclose(d.double(), exact, rtol=1e-4, atol=2e-2), names[index]
 
 
-# --------------------------------------------------------------- BASELINE configurations
+# --------------------------------------------------------------- the benchmark configurations
 
 def test_config1_small_default(capi, gpu, oracle):
     golden = np.load(GOLDEN / "torch_config1.npz")
