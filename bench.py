@@ -50,6 +50,7 @@ WORKLOADS = {
 }
 # Tall-K workload: K sharded over the ranks, partial products summed by an NCCL reduce-scatter.
 KSPLIT_WORKLOAD = "gemm_fp32_2048x262144x2048_ksplit"
+KSPLIT_FUSED_WORKLOAD = KSPLIT_WORKLOAD + "_fused"  # the reduction inside the kernel's epilogue (peer atomics)
 KSPLIT_SHAPE = (2048, 262144, 2048)
 # Few-rows (memory-bound) shapes of the tail sweep, k = n = 4096, entries U(-1, 1): one GPU streams B once.
 FEW_ROWS_WORKLOADS = {"gemm_fp32_1x4096x4096_fewrows": 1, "gemm_fp32_8x4096x4096_fewrows": 8,
@@ -162,7 +163,7 @@ def make_inputs(workload: str, rank: int, world: int, device):
 def workload_shape(workload: str):
     if workload in WORKLOADS:
         return WORKLOADS[workload][:3]
-    if workload == KSPLIT_WORKLOAD:
+    if workload in (KSPLIT_WORKLOAD, KSPLIT_FUSED_WORKLOAD):
         return KSPLIT_SHAPE
     return FEW_ROWS_WORKLOADS[workload], 4096, 4096
 
@@ -444,7 +445,14 @@ def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
     generator = torch.Generator(device=device).manual_seed(4 + rank)
     a = torch.rand(m, k_stop - k_start, device=device, generator=generator) * 2 - 1
     b = torch.rand(k_stop - k_start, n, device=device, generator=generator) * 2 - 1
-    if distributed:
+    if distributed and options.workload == KSPLIT_FUSED_WORKLOAD:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings, no NVLink multicast object
+        gemm = sharded.FusedKShardedGemm(m, n, k)
+
+        def step():
+            gemm(a, b, None, 1.0, 0.0)
+        primitive = "K-sharded: tensor kernel adding into the owners' rows over NVLink (no reduce-scatter)"
+    elif distributed:
         gemm = sharded.KShardedGemm(m, n, k)
         out = torch.empty(m // world, n, device=device)
 
@@ -491,7 +499,7 @@ def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
             "warmup": options.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": options.workload, "m": m, "k": k, "n": n, "k_per_gpu": k_stop - k_start,
-                       "partition": "K ranges per GPU; partial D summed by reduce-scatter over NVLink", "primitive": primitive,
+                       "partition": "K ranges per GPU; partial D summed over NVLink", "primitive": primitive,
                        "l2": "A and B shards (2 x 2 GiB in total) exceed the 126 MB L2"},
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": value / world / tensor_peak, "traffic": None,
@@ -510,7 +518,7 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD, SWEEP_WORKLOAD] + sorted(FEW_ROWS_WORKLOADS))
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + [KSPLIT_WORKLOAD, KSPLIT_FUSED_WORKLOAD, SWEEP_WORKLOAD] + sorted(FEW_ROWS_WORKLOADS))
     parser.add_argument("--no-extras", action="store_true", help="skip e2e, CPU baseline and plan-reuse legs")
     parser.add_argument("--primitive", default=None,
                         help="run this Primitive of the Plan instead of index 0 (per-primitive tier), e.g. Fp32Gemm")
@@ -540,7 +548,7 @@ def main() -> int:
     import flash_train.torch as ft_torch
     from flash_train.capi import GemmBinding, null_operand, tensor_operand
 
-    if options.workload == KSPLIT_WORKLOAD:
+    if options.workload in (KSPLIT_WORKLOAD, KSPLIT_FUSED_WORKLOAD):
         return run_k_split(options, torch, capi, world, rank, local_rank, device)
     if options.workload in FEW_ROWS_WORKLOADS:
         return run_few_rows(options, torch, capi, world, rank, local_rank, device)

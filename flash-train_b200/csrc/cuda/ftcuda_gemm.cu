@@ -81,3 +81,31 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
     if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
     return 0;
 }
+
+extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, float* const* owner_rows, int32_t owners,
+                                          uint64_t rows_per_owner, void* stream, char* message, size_t message_capacity) {
+    if (launch == nullptr || owner_rows == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null argument"); }
+    const LaunchState& state = *reinterpret_cast<const LaunchState*>(launch);
+    if (state.kernel != FTCUDA_GEMM_TF32X3 && state.kernel != FTCUDA_GEMM_TF32X3_SPLITK) {
+        return ftcuda::fail(message, message_capacity, 1, "scatter launches exist for the tensor-core kernels only");
+    }
+    if ((state.variant & ftcuda::kVariantFlagPair) != 0) {
+        return ftcuda::fail(message, message_capacity, 1, "the CTA-pair form has no scatter epilogue");
+    }
+    if (owners < 1 || owners > 8) { return ftcuda::fail(message, message_capacity, 1, "1 to 8 owners, got %d", owners); }
+    if (rows_per_owner == 0 || rows_per_owner >= (1ULL << 31) || rows_per_owner * static_cast<uint64_t>(owners) < state.desc.m) {
+        return ftcuda::fail(message, message_capacity, 1, "%d owners of %llu rows do not cover m = %llu", owners,
+                            static_cast<unsigned long long>(rows_per_owner), static_cast<unsigned long long>(state.desc.m));
+    }
+    for (int32_t i = 0; i < owners; ++i) {
+        if (owner_rows[i] == nullptr) { return ftcuda::fail(message, message_capacity, 1, "owner %d has no buffer", i); }
+    }
+    if (state.host_status != nullptr && *state.host_status != 0) {
+        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)",
+                            *state.host_status);
+    }
+    const cudaError_t error = ftcuda::launchTensorScatter(state, owner_rows, static_cast<std::uint32_t>(owners),
+                                                          static_cast<std::uint32_t>(rows_per_owner), static_cast<cudaStream_t>(stream));
+    if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+    return 0;
+}

@@ -540,7 +540,9 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     return 0;
 }
 
-cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream) {
+namespace {
+
+TensorParams makeTensorParams(const LaunchState& state) {
     const FtcudaGemmDesc& desc = state.desc;
     TensorParams p{};
     p.c              = desc.c;
@@ -562,9 +564,17 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     p.b_k_contiguous = (state.variant & kVariantFlagBk) != 0 ? 1U : 0U;
     p.alpha          = desc.alpha;
     p.beta           = desc.beta;
-    p.partials       = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
     p.status         = state.device_status;
-    cudaError_t error = cudaSuccess;
+    return p;
+}
+
+}  // namespace
+
+cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream) {
+    const FtcudaGemmDesc& desc = state.desc;
+    TensorParams p             = makeTensorParams(state);
+    p.partials                 = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
+    cudaError_t error          = cudaSuccess;
     if ((state.variant & kVariantFlagPair) != 0) {
         p.tiles_m      = static_cast<std::uint32_t>(ceilDiv(desc.m, 2 * kTileM));
         p.band_m_tiles = p.band_m_tiles > 1 ? p.band_m_tiles / 2 : 1;
@@ -581,6 +591,22 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     }
     countLaunches(launches);
     return error;
+}
+
+// One launch, no workspace, no reduction pass: every work item (output tile x K
+// slice) adds alpha * its sums into the owner's rows.
+cudaError_t launchTensorScatter(const LaunchState& state, float* const* owner_rows, std::uint32_t owners,
+                                std::uint32_t rows_per_owner, cudaStream_t stream) {
+    TensorParams p = makeTensorParams(state);
+    p.c            = nullptr;
+    p.beta         = 0.0F;
+    p.partials     = nullptr;
+    p.scatter_rows = rows_per_owner;
+    for (std::uint32_t i = 0; i < owners && i < 8; ++i) { p.scatter[i] = owner_rows[i]; }
+    const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
+    tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+    countLaunches(1);
+    return cudaGetLastError();
 }
 
 }  // namespace ftcuda

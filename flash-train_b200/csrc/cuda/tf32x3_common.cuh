@@ -27,6 +27,11 @@ struct TensorParams {
     std::uint32_t b_k_contiguous;  // B was given contiguous along K (a transposed view): raw tile is [n][k], swizzled
     float alpha, beta;
     float* partials;  // non-null: raw sums to partials[split][m][n]
+    // Scatter mode (scatter_rows != 0): alpha * sum is ADDED, element by element,
+    // into the buffer of the row's owner -- dense [scatter_rows][n] matrices that
+    // may live on other GPUs (peer-mapped) -- instead of being written to d.
+    float* scatter[8];
+    std::uint32_t scatter_rows;
     int* status;
 };
 
@@ -84,10 +89,26 @@ static __device__ __noinline__ void writeRowSegmentSlow(float* out, std::int64_t
     }
 }
 
+// Scatter mode: adds scale * sum[j] to target[j] for the (up to 16) columns left in the row. K slices of
+// this GPU and of other GPUs all add into the owner's rows; the order of the additions is not fixed.
+static __device__ __noinline__ void addRowSegment(float* target, float scale, std::uint32_t columns_left, const float* sum) {
+    for (std::uint32_t j = 0; j < 16 && j < columns_left; ++j) { atomicAdd(target + j, scale * sum[j]); }
+}
+
 // Writes one row segment of 16 consecutive columns held by one thread.
 __device__ __forceinline__ void writeRowSegment(const TensorParams& p, const WorkItem& w, std::uint32_t row,
                                                 std::uint32_t col, const float (&sum)[16], bool vector_ok) {
     if (row >= p.m || col >= p.n) { return; }
+    if (p.scatter_rows != 0) {
+        // Out of line, through a local copy: the common path keeps its registers.
+        const std::uint32_t owner = row / p.scatter_rows;
+        float copy[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { copy[j] = sum[j]; }
+        addRowSegment(p.scatter[owner] + static_cast<std::uint64_t>(row - owner * p.scatter_rows) * p.n + col, p.alpha,
+                      p.n - col, copy);
+        return;
+    }
     const bool partial = p.partials != nullptr;
     float* out         = partial ? p.partials + static_cast<std::uint64_t>(w.split) * p.m * p.n : p.d;
     const std::int64_t out_row_stride = partial ? p.n : p.d_row_stride;

@@ -49,7 +49,7 @@ EXPORTED_SYMBOLS = (
 PLATFORM_SYMBOLS = (
     "ftcuda_current_device ftcuda_device_sm_count ftcuda_gemm_supports ftcuda_gemm_configure "
     "ftcuda_gemm_workspace_bytes ftcuda_gemm_launch ftcuda_launch_count ftcuda_trace_push ftcuda_trace_pop "
-    "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity"
+    "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity ftcuda_gemm_launch_scatter"
 ).split()
 
 
@@ -407,10 +407,11 @@ def _declare_platform(lib) -> None:
     lib.ftcuda_gemm_workspace_bytes.restype = c_uint64
     lib.ftcuda_gemm_launch.argtypes = [POINTER(GemmLaunch), c_void_p, c_uint64, c_void_p] + message
     lib.ftcuda_gemm_splitk_static.argtypes = [POINTER(GemmDesc), c_void_p] + message
+    lib.ftcuda_gemm_launch_scatter.argtypes = [POINTER(GemmLaunch), POINTER(c_void_p), ctypes.c_int32, c_uint64, c_void_p] + message
     lib.ftcuda_gemm_splitk_static_capacity.argtypes = []
     lib.ftcuda_gemm_splitk_static_capacity.restype = c_uint64
     for name in ("ftcuda_current_device", "ftcuda_device_sm_count", "ftcuda_gemm_supports", "ftcuda_gemm_configure",
-                 "ftcuda_gemm_launch", "ftcuda_gemm_splitk_static"):
+                 "ftcuda_gemm_launch", "ftcuda_gemm_splitk_static", "ftcuda_gemm_launch_scatter"):
         getattr(lib, name).restype = ctypes.c_int
 
 
@@ -443,6 +444,16 @@ class PlatformGemm:
         buffer = ctypes.create_string_buffer(256)
         if lib.ftcuda_gemm_launch(byref(self.launch), c_void_p(workspace), workspace_bytes, c_void_p(stream), buffer,
                                   256) != 0:
+            raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
+
+
+    def run_scatter(self, owner_rows, rows_per_owner: int, stream: int = 0) -> None:
+        """ftcuda_gemm_launch_scatter: add alpha * (A B) into the row buffers of the rows' owners
+        (device addresses, possibly peer-mapped); tensor-core families only."""
+        pointers = (c_void_p * len(owner_rows))(*[c_void_p(int(pointer)) for pointer in owner_rows])
+        buffer = ctypes.create_string_buffer(256)
+        if lib.ftcuda_gemm_launch_scatter(byref(self.launch), pointers, len(owner_rows), rows_per_owner, c_void_p(stream),
+                                          buffer, 256) != 0:
             raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
 
 

@@ -15,6 +15,12 @@ creates its own Plan on its own device:
                    [r*m/world, (r+1)*m/world) of D, and the owner adds beta * C
                    to its rows exactly once, after the sum.
 
+  FusedKShardedGemm  the same partitioning without the reduce-scatter pass: the
+                   tensor-core kernel of every rank ADDS its results straight
+                   into the rows' owners' buffers over NVLink (peer-mapped
+                   symmetric memory, FP32 atomics), so the reduction is part of
+                   the GEMM's epilogue and no m x n partial is ever stored.
+
 Process-group plumbing is torch.distributed (NCCL over NVLink on GPUs). The
 local product is a Plan of libflash_train.so executed on torch's current
 stream; `local_gemm` can be replaced by another callable with the same
@@ -150,3 +156,76 @@ class KShardedGemm:
         if c_rows is not None and beta != 0.0:
             out.add_(c_rows, alpha=beta)
         return out
+
+
+class FusedKShardedGemm:
+    """K-sharded GEMM whose reduction across ranks happens inside the kernel's epilogue.
+
+    Every rank owns rows [rank * m / world, (rank + 1) * m / world) of D in a buffer of symmetric
+    memory (torch.distributed._symmetric_memory), so that every rank holds a peer-mapped address of
+    every other rank's rows. A call: the owner writes beta * C (or zeros) into its rows; a barrier;
+    every rank launches the tensor-core kernel on its K range through ftcuda_gemm_launch_scatter,
+    whose epilogue adds alpha * (A_r B_r) into the owners' rows with FP32 atomics over NVLink; a
+    barrier; the rows are complete. No partial matrix, no reduce-scatter, no workspace. The order of
+    the additions is not fixed: results agree with the reduce-scatter form to rounding, not bitwise.
+
+    Operands must suit the tensor-core kernels (16-byte aligned bases and pitches).
+    """
+
+    def __init__(self, m: int, n: int, k: int, group=None, device=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symmetric_memory
+
+        from . import capi
+
+        self._capi = capi
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if m % self.world != 0:
+            raise ValueError(f"m = {m} is not divisible by {self.world} ranks")
+        if self.world > 8:
+            raise ValueError("at most 8 owners")
+        self.m, self.n, self.k = m, n, k
+        self.rows = m // self.world
+        self.k_start, self.k_stop = k_range(k, self.world, self.rank)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.out = symmetric_memory.empty((self.rows, n), dtype=torch.float32, device=self.device)
+        self._handle = symmetric_memory.rendezvous(self.out, self.group)
+        self._owner_rows = [int(self._handle.buffer_ptrs[r]) for r in range(self.world)]
+        self._launches = {}
+
+    def _launch_for(self, a_cols, b_rows, alpha: float):
+        capi = self._capi
+        key = (a_cols.data_ptr(), b_rows.data_ptr(), tuple(a_cols.stride()), tuple(b_rows.stride()), float(alpha))
+        launch = self._launches.get(key)
+        if launch is None:
+            operand = lambda t: (t.data_ptr(), tuple(t.shape), None if t.is_contiguous() else tuple(t.stride()))  # noqa: E731
+            # The descriptor's output is not written in scatter mode; it only carries the shape.
+            desc = capi.make_desc(operand(a_cols), operand(b_rows), (0, (self.m, self.n), None),
+                                  (self.out.data_ptr(), (self.m, self.n), None), alpha, 0.0, self.device.index or 0)
+            kernel = capi.KERNEL_TF32X3_SPLITK if capi.platform_supports(capi.KERNEL_TF32X3_SPLITK, desc) is None \
+                else capi.KERNEL_TF32X3
+            launch = capi.PlatformGemm(kernel, desc)
+            self._launches[key] = launch
+        return launch
+
+    def __call__(self, a_cols, b_rows, c_rows=None, alpha: float = 1.0, beta: float = 0.0):
+        """Returns this rank's rows of D (the symmetric buffer itself: copy it before the next call)."""
+        import torch
+
+        depth = self.k_stop - self.k_start
+        if a_cols.shape != (self.m, depth) or b_rows.shape != (depth, self.n):
+            raise ValueError(f"this rank owns K range [{self.k_start}, {self.k_stop}): expected A {self.m}x{depth} "
+                             f"and B {depth}x{self.n}")
+        if c_rows is not None and beta != 0.0:
+            torch.mul(c_rows, beta, out=self.out)
+        else:
+            self.out.zero_()
+        self._handle.barrier()  # every owner's rows are initialised before anybody adds to them
+        if depth > 0:
+            launch = self._launch_for(a_cols, b_rows, alpha)
+            launch.run_scatter(self._owner_rows, self.rows, torch.cuda.current_stream(self.device).cuda_stream)
+        self._handle.barrier()  # every rank's additions have been issued and are complete
+        return self.out

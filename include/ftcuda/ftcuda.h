@@ -128,6 +128,25 @@ FTCUDA_API int ftcuda_gemm_splitk_static(const FtcudaGemmDesc* desc, void* strea
                                          size_t message_capacity);
 FTCUDA_API uint64_t ftcuda_gemm_splitk_static_capacity(void);
 
+/*
+ * K-sharded GEMM over several GPUs without a separate reduction pass (no
+ * counterpart in the reference, which is single-device): `launch` was
+ * configured for FTCUDA_GEMM_TF32X3 or FTCUDA_GEMM_TF32X3_SPLITK on this GPU's
+ * shard of K; instead of writing d, the kernel ADDS alpha * (A B) into the
+ * buffers of the rows' owners: row r goes to owner r / rows_per_owner, whose
+ * buffer owner_rows[owner] is a dense FP32 [rows_per_owner][n] matrix. The
+ * buffers may live on other GPUs (peer-mapped addresses, e.g. symmetric
+ * memory); the additions are single FP32 atomics travelling over NVLink. The
+ * caller initialises every buffer (zeros, or beta * C) and orders that before
+ * the launch, and the launches of all GPUs before the first read, with
+ * barriers of its own. c and beta of the descriptor are ignored; no workspace
+ * is needed even for the split-K family (its K slices add directly). The order
+ * of the additions is not fixed, so the last bits of the result can differ
+ * from run to run.
+ */
+FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, float* const* owner_rows, int32_t owners,
+                                          uint64_t rows_per_owner, void* stream, char* message, size_t message_capacity);
+
 /* Number of device kernels ftcuda_gemm_launch has enqueued from this process;
  * benchmarks read it to report how many launches a timed region made. */
 FTCUDA_API uint64_t ftcuda_launch_count(void);

@@ -461,3 +461,42 @@ def test_few_rows_kernel_with_b_contiguous_along_k(capi, gpu, oracle, m):
     d, names = gpu.gemm(x, w.t())
     assert names[0] == "Fp32GemmSkinny", names
     check_against_float64(oracle, d, x, w.t().contiguous(), None, 1.0, 0.0, f"x @ W^T via {names[0]}")
+
+
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_scatter_launch_adds_rows_into_owner_buffers(capi, gpu, oracle, kernel):
+    """ftcuda_gemm_launch_scatter with the owners' buffers on this GPU: two K shards ("ranks") add
+    their products into three owners' row blocks that were initialised with beta * C."""
+    import os
+
+    if os.environ.get("FT_SKIP_TENSOR"):
+        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
+    torch.manual_seed(47)
+    m, k, n, owners = 384, 4608, 400, 3
+    rows = m // owners
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(k, n, device="cuda")
+    c = torch.randn(m, n, device="cuda")
+    alpha, beta = 0.75, -1.25
+    blocks = [(beta * c[i * rows:(i + 1) * rows]).contiguous() for i in range(owners)]
+    for k_start, k_stop in ((0, 2304), (2304, 4608)):
+        a_cols = a[:, k_start:k_stop].contiguous()
+        b_rows = b[k_start:k_stop].contiguous()
+        unused = torch.empty(m, n, device="cuda")
+        desc = capi.make_desc(gpu.operand(a_cols), gpu.operand(b_rows), capi.null_operand(m, n), gpu.operand(unused), alpha, 0.0,
+                              torch.cuda.current_device())
+        reason = capi.platform_supports(kernel, desc)
+        if reason is not None:
+            pytest.skip(reason)
+        launch = capi.PlatformGemm(kernel, desc)
+        launch.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream())
+    torch.cuda.synchronize()
+    check_against_float64(oracle, torch.cat(blocks), a, b, c, alpha, beta, f"scatter launch, {capi.KERNEL_NAMES[kernel]}")
+    # Argument checks: owners must cover m, buffers must exist, only tensor-core families scatter.
+    with pytest.raises(capi.FTrainError, match="do not cover"):
+        launch.run_scatter([blocks[0].data_ptr()], rows, gpu.current_stream())
+    with pytest.raises(capi.FTrainError, match="no buffer"):
+        launch.run_scatter([blocks[0].data_ptr(), 0, blocks[2].data_ptr()], rows, gpu.current_stream())
+    simt = capi.PlatformGemm(capi.KERNEL_SIMT, desc)
+    with pytest.raises(capi.FTrainError, match="tensor-core kernels only"):
+        simt.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream())

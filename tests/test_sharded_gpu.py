@@ -17,7 +17,8 @@ REPO = Path(__file__).resolve().parents[1]
 def worker(rank, world, port, failures):
     for entry in (str(REPO), str(REPO / "flash-train_b200" / "python")):
         sys.path.insert(0, entry)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    # No NVLink multicast objects anywhere: NCCL without NVLS, symmetric memory without multicast.
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
@@ -45,6 +46,18 @@ def worker(rank, world, port, failures):
     torch.cuda.synchronize()
     if not torch.allclose(d_split.double(), exact[split.row_start:split.row_stop], rtol=1e-4, atol=2e-2):
         failures.append(f"rank {rank}: K-sharded result is off")
+    # The same K-sharded product with the reduction fused into the kernel's epilogue: every rank adds
+    # its results into the owners' rows through peer-mapped symmetric memory.
+    try:
+        fused = sharded.FusedKShardedGemm(m, n, k)
+        for _ in range(2):  # the second call reuses the symmetric buffer
+            d_fused = fused(a[:, fused.k_start:fused.k_stop].contiguous(), b[fused.k_start:fused.k_stop].contiguous(),
+                            c[split.row_start:split.row_stop].contiguous(), 1.25, -0.5)
+            torch.cuda.synchronize()
+            if not torch.allclose(d_fused.double(), exact[split.row_start:split.row_stop], rtol=1e-4, atol=2e-2):
+                failures.append(f"rank {rank}: fused K-sharded result is off")
+    except Exception as error:  # noqa: BLE001 - reported to the parent, the process leaves in order
+        failures.append(f"rank {rank}: fused K-sharded GEMM raised {type(error).__name__}: {error}")
     dist.barrier()
     dist.destroy_process_group()
 
