@@ -427,19 +427,26 @@ std::uint32_t chooseSplits(std::uint64_t tiles, std::uint64_t k, int sms) {
     return best;
 }
 
-// K blocks accumulated inside the tensor core between two drains. 4 blocks =
-// 128 K elements: measured on B200, the scaled error against float64 is then
-// about 0.4x that of an FP32 FFMA GEMM at K = 4096 and 1.1x at K = 512, for
-// about 1 % of throughput; without drains it is 12x at K = 4096 and 47x at
-// K = 65536, because the tensor core's FP32 accumulation truncates. FTCUDA_TF32_CHUNK_K_BLOCKS overrides it (a tuning knob for
-// accuracy/throughput experiments; read at Plan creation).
-std::uint32_t chunkKBlocks() {
+// K blocks accumulated inside the tensor core between two drains. The tensor
+// core's FP32 accumulation truncates, so the error of an undrained chain grows
+// with its length: measured on B200, the scaled error against float64,
+// relative to that of an FP32 FFMA GEMM on the same inputs, is about
+// 6 * L / sqrt(K) for a drain every L K blocks (L = 4: 1.08 at K = 512, 0.39 at
+// K = 4096; L = 8: 0.82 at K = 4096, 0.18 at K = 65536; never: 12 at K = 4096,
+// 47 at K = 65536). A drain stalls the MMAs for about 0.6 us, so L should be as
+// long as accuracy allows: L = sqrt(K) / 12.5 aims at half the FFMA GEMM's
+// error whatever K is -- 2 at K = 1000, 5 at K = 4096, 16 (the cap) from
+// K = 40000 on. FTCUDA_TF32_CHUNK_K_BLOCKS overrides it (a knob for
+// accuracy/throughput experiments; read when a launch is configured).
+std::uint32_t chunkKBlocks(std::uint64_t k) {
     const char* text = std::getenv("FTCUDA_TF32_CHUNK_K_BLOCKS");
     if (text != nullptr) {
         const long value = std::strtol(text, nullptr, 10);
         if (value >= 1 && value <= (1L << 20)) { return static_cast<std::uint32_t>(value); }
     }
-    return 4;
+    std::uint32_t blocks = 1;
+    while (blocks < 16 && static_cast<std::uint64_t>(blocks + 1) * (blocks + 1) * 156 <= k) { ++blocks; }  // 12.5^2 = 156.25
+    return blocks;
 }
 
 // Output tiles are walked in bands of this many M tiles (all N tiles of a band
@@ -461,7 +468,10 @@ const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
     if (desc.m >= (1ULL << 31) || desc.n >= (1ULL << 31) || desc.k >= (1ULL << 31)) {
         return "an extent does not fit 31 bits";
     }
-    if (desc.k < 32) { return "K is shorter than one K block"; }
+    // Even one K block is twelve truncating accumulations inside the tensor core;
+    // against a sum of so few products that error shows (measured: up to 2.3x an
+    // FFMA GEMM's at K = 32), so short K is left to the exact kernels.
+    if (desc.k < 128) { return "K is too short for the split-precision kernel (under 128)"; }
     if (!tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m) &&
         !tmaEligible(desc.a, desc.a_row_stride, desc.a_col_stride, desc.m, desc.k)) {
         return "A is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
@@ -502,7 +512,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
         state.grid_x          = static_cast<std::uint32_t>(2 * (pair_items < pairs ? pair_items : pairs));
         state.grid_y          = 1;
         state.grid_z          = 1;
-        state.chunk_k_blocks  = chunkKBlocks();
+        state.chunk_k_blocks  = chunkKBlocks(desc.k);
         state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
         return configureTensorPair(state, message, capacity);
     }
@@ -512,7 +522,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     state.grid_z              = 1;
     state.block               = kThreads;
     state.smem_bytes          = kSmemBytes;
-    state.chunk_k_blocks      = chunkKBlocks();
+    state.chunk_k_blocks      = chunkKBlocks(desc.k);
     state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
     const bool a_encoded =
         (state.variant & kVariantMaskA) == kVariantTmaAk

@@ -500,3 +500,43 @@ def test_scatter_launch_adds_rows_into_owner_buffers(capi, gpu, oracle, kernel):
     simt = capi.PlatformGemm(capi.KERNEL_SIMT, desc)
     with pytest.raises(capi.FTrainError, match="tensor-core kernels only"):
         simt.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream())
+
+
+def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle):
+    """Sixty seeded random problems: extents off every tile size, A and B plain or as transposed views
+    (pitches padded to keep them 16-byte aligned or deliberately not), C present or not, assorted
+    scalars. Every family that accepts a problem must meet the float64 bar on it; the exact-FP32
+    families are also held to the reference's tolerance against the sequential oracle when K is short."""
+    import random
+
+    rng = random.Random(20240611)
+    torch.manual_seed(53)
+    ran = {name: 0 for name in capi.KERNEL_NAMES.values()}
+    for case in range(60):
+        m = rng.choice([1, 2, 7, 17, 31, 33, 64, 100, 129, 200, 257, 384, 513])
+        n = rng.choice([1, 5, 32, 96, 100, 128, 131, 192, 260, 384, 500, 777])
+        k = rng.choice([1, 8, 31, 32, 33, 64, 100, 256, 300, 512, 1000, 2048, 4100])
+        a_t, b_t = rng.random() < 0.35, rng.random() < 0.35
+        pad_a, pad_b = rng.choice([0, 0, 4, 3]), rng.choice([0, 0, 4, 1])
+        a = (torch.randn(k, m + pad_a, device="cuda")[:, :m].t() if a_t else torch.randn(m, k + pad_a, device="cuda")[:, :k])
+        b = (torch.randn(n, k + pad_b, device="cuda")[:, :k].t() if b_t else torch.randn(k, n + pad_b, device="cuda")[:, :n])
+        c = torch.randn(m, n, device="cuda") if rng.random() < 0.6 else None
+        alpha = rng.choice([1.0, -0.5, 2.25])
+        beta = rng.choice([0.0, 1.0, -1.75]) if c is not None else 0.0
+        for kernel, name in capi.KERNEL_NAMES.items():
+            d, reason = platform_gemm(capi, gpu, kernel, a, b, c, alpha, beta)
+            if d is None:
+                continue
+            ran[name] += 1
+            what = f"case {case}: {name} {m}x{k}x{n} a_t={a_t} b_t={b_t} pads=({pad_a},{pad_b}) alpha={alpha} beta={beta}"
+            if k <= 300 or kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK, capi.KERNEL_SKINNY, capi.KERNEL_SIMT_SPLITK):
+                # Blocked sums (or short K): the float64 bar applies as it stands.
+                check_against_float64(oracle, d, a.contiguous(), b.contiguous(), c, alpha, beta, what)
+            else:
+                # A strictly sequential FP32 sum over a long K: the reference's own tolerance, scaled as in the smoke test.
+                exact = alpha * (a.double() @ b.double()) + (beta * c.double() if c is not None else 0.0)
+                slack = 2e-5 * max(1.0, (k / 257.0) ** 0.5)
+                scale = (a.double().abs() @ b.double().abs()) * abs(alpha) + (abs(beta) * c.double().abs() if c is not None else 0.0)
+                assert ((d.double() - exact).abs() <= slack * (1.0 + scale)).all(), what
+    # The draw must actually have exercised every family.
+    assert all(count >= 5 for count in ran.values()), ran
