@@ -21,6 +21,13 @@ from pinned host memory to the device, runs the GEMM and copies D back to the
 host. The call moves A, C and D in bands of rows so that copy-in, kernels and
 copy-out of successive bands overlap; all of it is inside the timed region.
 
+Other workloads (--workload): the 4096^3 GEMM with addend; the default shape with B as a transposed view
+(`_bt`); the few-rows shapes m = 1 / 8 / 17 with k = n = 4096 (`_fewrows`, HBM-bound, B rotating over four
+matrices; `_fewrows_bt` with B as the transposed view of a weight matrix); the tall-K GEMM sharded along K
+over the GPUs, reduced by NCCL reduce-scatter (`_ksplit`) or inside the kernel's epilogue over peer memory
+(`_ksplit_fused`); and `finder_sweep`, which times every kernel family on a grid of shapes against the
+Finder's choice.
+
 `--impl reference` times the reference's own CPU implementation of the path --
 its PyTorch reference expression alpha*(a@b)+beta*c on CPU tensors -- on the
 host cores, each step a bounded row-slice of the same workload.

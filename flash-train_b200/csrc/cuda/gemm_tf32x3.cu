@@ -35,11 +35,13 @@
 //   warps 8-15  drain / epilogue. Every `chunk_k_blocks` K blocks the chunk
 //               accumulator is added, in round-to-nearest FP32, to a running
 //               sum kept in TMEM columns 192-383, and the chunk restarts from
-//               zero (default: every 4 K blocks). This bounds the length of any
-//               accumulation chain inside the tensor core, whose internal FP32
-//               additions truncate. After the last chunk the sum is scaled and
-//               written out (or stored raw as a split-K partial) while the next
-//               tile's first chunk is already being multiplied.
+//               zero (the interval grows with sqrt(K), see chunkKBlocks). This
+//               bounds the length of any accumulation chain inside the tensor
+//               core, whose internal FP32 additions truncate. After the last
+//               chunk the sum is scaled and written out -- or stored raw as a
+//               split-K partial, or added into the rows' owners' buffers
+//               (scatter launches) -- while the next tile's first chunk is
+//               already being multiplied.
 //
 // Shared memory: 3 raw slots x 40 KiB + 2 stages x (B_hi 24 + B_lo 24 KiB) =
 // 216 KiB. Tensor memory: chunk 192 + running 192 + 2 stages x (A_hi 32 +
