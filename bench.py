@@ -102,7 +102,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -141,6 +141,22 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima), "reasons": sorted(reasons),
                 "samples": len(clocks)}
+
+
+def clocks_under_load(sampler: "ClockSampler", device_index: int, step, torch, elapsed_ms: float, steps: int) -> dict:
+    """The sampler's summary; when the timed region (elapsed_ms, already the maximum over ranks, so every
+    rank decides alike) was too short for nvidia-smi to deliver samples, every rank repeats the same
+    step for about 0.4 s (untimed, after the measurement) under a second sampler."""
+    if elapsed_ms >= 200.0:
+        return sampler.summary()
+    repeats = max(1, int(400.0 / max(elapsed_ms / max(steps, 1), 1e-3)))
+    with ClockSampler(device_index) as extra:
+        for _ in range(repeats):
+            step()
+        torch.cuda.synchronize()
+    summary = extra.summary()
+    summary["note"] = "timed region shorter than the sampling period: sampled while repeating the step right after it"
+    return summary
 
 
 def make_inputs(workload: str, rank: int, world: int, device):
@@ -412,6 +428,7 @@ def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
         slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         elapsed_ms = float(slowest.item())
+    clocks = clocks_under_load(sampler, local_rank, step, torch, elapsed_ms, options.steps)
     if rank == 0:
         gemms = options.steps * FEW_ROWS_COPIES
         ms_per_gemm = elapsed_ms / gemms
@@ -431,7 +448,7 @@ def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
                          "frac": achieved / peaks["hbm_gbs"], "traffic": MEASURED_DRAM_TRAFFIC.get((options.workload, primitive, 1)),
                          "algorithmic_bytes": algorithmic, "peak_source": f"{peaks['source']} hbm_gbs (copy)",
                          "kernel": "skinnyGemm", "us_per_launch": ms_per_gemm * 1e3},
-            "clocks": sampler.summary(), "gpu_launches": launches,
+            "clocks": clocks, "gpu_launches": launches,
         }
         print(json.dumps(line), flush=True)
     if distributed:
@@ -496,6 +513,7 @@ def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
         slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         elapsed_ms = float(slowest.item())
+    clocks = clocks_under_load(sampler, local_rank, step, torch, elapsed_ms, options.steps)
     if rank == 0:
         ms_per_step = elapsed_ms / options.steps
         value = 2.0 * m * n * k / (ms_per_step * 1e-3) / 1e12
@@ -511,7 +529,7 @@ def run_k_split(options, torch, capi, world, rank, local_rank, device) -> int:
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": value / world / tensor_peak, "traffic": None,
                          "peak_source": f"{peaks['source']} bf16_tflops_sustained / 6"},
-            "clocks": sampler.summary(), "gpu_launches": launches,
+            "clocks": clocks, "gpu_launches": launches,
         }
         print(json.dumps(line), flush=True)
     if distributed:
@@ -599,11 +617,11 @@ def main() -> int:
         barrier()
         elapsed_ms = start_event.elapsed_time(end_event)
     launches = capi.launch_count() - launches_before
-    clocks = sampler.summary()
     if distributed:
         slowest = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         elapsed_ms = float(slowest.item())
+    clocks = clocks_under_load(sampler, local_rank, step, torch, elapsed_ms, options.steps)
     ms_per_step = elapsed_ms / options.steps
     total_flops = 2.0 * m * n * k
     value = total_flops / (ms_per_step * 1e-3) / 1e12
