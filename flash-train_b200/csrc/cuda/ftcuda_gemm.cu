@@ -82,8 +82,9 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
     return 0;
 }
 
-extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, float* const* owner_rows, int32_t owners,
-                                          uint64_t rows_per_owner, void* stream, char* message, size_t message_capacity) {
+extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                          float* const* owner_rows, int32_t owners, uint64_t rows_per_owner, void* stream,
+                                          char* message, size_t message_capacity) {
     if (launch == nullptr || owner_rows == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null argument"); }
     const LaunchState& state = *reinterpret_cast<const LaunchState*>(launch);
     if (state.kernel != FTCUDA_GEMM_TF32X3 && state.kernel != FTCUDA_GEMM_TF32X3_SPLITK) {
@@ -104,7 +105,9 @@ extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, float*
         return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)",
                             *state.host_status);
     }
-    const cudaError_t error = ftcuda::launchTensorScatter(state, owner_rows, static_cast<std::uint32_t>(owners),
+    // A workspace is optional here; one that is too small is ignored (direct adds).
+    if (workspace_bytes < state.workspace_bytes) { workspace = nullptr; }
+    const cudaError_t error = ftcuda::launchTensorScatter(state, workspace, owner_rows, static_cast<std::uint32_t>(owners),
                                                           static_cast<std::uint32_t>(rows_per_owner), static_cast<cudaStream_t>(stream));
     if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
     return 0;

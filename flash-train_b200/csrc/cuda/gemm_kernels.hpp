@@ -104,8 +104,12 @@ const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k);
 int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t capacity);
 cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream);
 // The tensor kernel with its results added into per-owner row buffers (see ftcuda_gemm_launch_scatter).
-cudaError_t launchTensorScatter(const LaunchState& state, float* const* owner_rows, std::uint32_t owners,
+// With a workspace (and K slices) the slices are combined locally first and every element travels once.
+cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float* const* owner_rows, std::uint32_t owners,
                                 std::uint32_t rows_per_owner, cudaStream_t stream);
+cudaError_t launchSplitKReduceScatter(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,
+                                      float* const* owner_rows, std::uint32_t owners, std::uint32_t rows_per_owner,
+                                      cudaStream_t stream);
 
 // D = alpha * sum_s partial[s] + beta * C over `splits` dense m x n partials.
 cudaError_t launchSplitKReduce(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,

@@ -66,6 +66,29 @@ __global__ void __launch_bounds__(256) splitKReduce(const ReduceParams p) {
     }
 }
 
+// Scatter form: the combined value of every element is ADDED (one FP32 atomic) into the buffer of the
+// row's owner, a dense [rows_per_owner][n] matrix that may live on another GPU.
+struct ScatterReduceParams {
+    const float* partials;
+    float* owner_rows[8];
+    std::uint64_t m, n, rows_per_owner;
+    std::uint32_t splits;
+    float alpha;
+};
+
+__global__ void __launch_bounds__(256) splitKReduceScatter(const ScatterReduceParams p) {
+    const std::uint64_t slab   = p.m * p.n;
+    const std::uint64_t stride = static_cast<std::uint64_t>(gridDim.x) * blockDim.x;
+    for (std::uint64_t index = static_cast<std::uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < slab; index += stride) {
+        float sum = p.partials[index];
+        for (std::uint32_t s = 1; s < p.splits; ++s) { sum += p.partials[s * slab + index]; }
+        const std::uint64_t row   = index / p.n;
+        const std::uint64_t col   = index % p.n;
+        const std::uint64_t owner = row / p.rows_per_owner;
+        atomicAdd(p.owner_rows[owner] + (row - owner * p.rows_per_owner) * p.n + col, p.alpha * sum);
+    }
+}
+
 bool denseAligned(const float* base, std::int64_t row_stride, std::int64_t col_stride) {
     return col_stride == 1 && row_stride % 4 == 0 && reinterpret_cast<std::uintptr_t>(base) % 16 == 0;
 }
@@ -95,6 +118,29 @@ cudaError_t launchSplitKReduce(const FtcudaGemmDesc& desc, const float* partials
     if (blocks > 148 * 16) { blocks = 148 * 16; }
     if (blocks == 0) { blocks = 1; }
     splitKReduce<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace ftcuda
+
+namespace ftcuda {
+
+cudaError_t launchSplitKReduceScatter(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,
+                                      float* const* owner_rows, std::uint32_t owners, std::uint32_t rows_per_owner,
+                                      cudaStream_t stream) {
+    ScatterReduceParams p{};
+    p.partials       = partials;
+    p.m              = desc.m;
+    p.n              = desc.n;
+    p.rows_per_owner = rows_per_owner;
+    p.splits         = splits;
+    p.alpha          = desc.alpha;
+    for (std::uint32_t i = 0; i < owners && i < 8; ++i) { p.owner_rows[i] = owner_rows[i]; }
+    const std::uint64_t elements = desc.m * desc.n;
+    std::uint64_t blocks         = (elements + 255) / 256;
+    if (blocks > 148ULL * 16) { blocks = 148ULL * 16; }
+    if (blocks == 0) { return cudaSuccess; }
+    splitKReduceScatter<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -605,20 +605,31 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
     return error;
 }
 
-// One launch, no workspace, no reduction pass: every work item (output tile x K
-// slice) adds alpha * its sums into the owner's rows.
-cudaError_t launchTensorScatter(const LaunchState& state, float* const* owner_rows, std::uint32_t owners,
+// Without a workspace: one launch, every work item (output tile x K slice) adds
+// alpha * its sums into the owner's rows. With a workspace and several K slices:
+// the slices are written as partials, combined locally and added once per element.
+cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float* const* owner_rows, std::uint32_t owners,
                                 std::uint32_t rows_per_owner, cudaStream_t stream) {
     TensorParams p = makeTensorParams(state);
     p.c            = nullptr;
     p.beta         = 0.0F;
-    p.partials     = nullptr;
-    p.scatter_rows = rows_per_owner;
-    for (std::uint32_t i = 0; i < owners && i < 8; ++i) { p.scatter[i] = owner_rows[i]; }
+    const bool two_pass = workspace != nullptr && state.splits > 1;
+    p.partials          = two_pass ? static_cast<float*>(workspace) : nullptr;
+    if (!two_pass) {
+        p.scatter_rows = rows_per_owner;
+        for (std::uint32_t i = 0; i < owners && i < 8; ++i) { p.scatter[i] = owner_rows[i]; }
+    }
     const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
     tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
-    countLaunches(1);
-    return cudaGetLastError();
+    cudaError_t error      = cudaGetLastError();
+    std::uint64_t launches = 1;
+    if (error == cudaSuccess && two_pass) {
+        error = launchSplitKReduceScatter(state.desc, static_cast<const float*>(workspace), state.splits, owner_rows, owners,
+                                          rows_per_owner, stream);
+        ++launches;
+    }
+    countLaunches(launches);
+    return error;
 }
 
 }  // namespace ftcuda

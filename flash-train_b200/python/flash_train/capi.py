@@ -407,7 +407,8 @@ def _declare_platform(lib) -> None:
     lib.ftcuda_gemm_workspace_bytes.restype = c_uint64
     lib.ftcuda_gemm_launch.argtypes = [POINTER(GemmLaunch), c_void_p, c_uint64, c_void_p] + message
     lib.ftcuda_gemm_splitk_static.argtypes = [POINTER(GemmDesc), c_void_p] + message
-    lib.ftcuda_gemm_launch_scatter.argtypes = [POINTER(GemmLaunch), POINTER(c_void_p), ctypes.c_int32, c_uint64, c_void_p] + message
+    lib.ftcuda_gemm_launch_scatter.argtypes = [POINTER(GemmLaunch), c_void_p, c_uint64, POINTER(c_void_p), ctypes.c_int32, c_uint64,
+                                               c_void_p] + message
     lib.ftcuda_gemm_splitk_static_capacity.argtypes = []
     lib.ftcuda_gemm_splitk_static_capacity.restype = c_uint64
     for name in ("ftcuda_current_device", "ftcuda_device_sm_count", "ftcuda_gemm_supports", "ftcuda_gemm_configure",
@@ -447,13 +448,14 @@ class PlatformGemm:
             raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
 
 
-    def run_scatter(self, owner_rows, rows_per_owner: int, stream: int = 0) -> None:
+    def run_scatter(self, owner_rows, rows_per_owner: int, stream: int = 0, workspace: int = 0, workspace_bytes: int = 0) -> None:
         """ftcuda_gemm_launch_scatter: add alpha * (A B) into the row buffers of the rows' owners
-        (device addresses, possibly peer-mapped); tensor-core families only."""
+        (device addresses, possibly peer-mapped); tensor-core families only. With a workspace of
+        self.workspace_bytes the K slices are combined locally before they travel."""
         pointers = (c_void_p * len(owner_rows))(*[c_void_p(int(pointer)) for pointer in owner_rows])
         buffer = ctypes.create_string_buffer(256)
-        if lib.ftcuda_gemm_launch_scatter(byref(self.launch), pointers, len(owner_rows), rows_per_owner, c_void_p(stream),
-                                          buffer, 256) != 0:
+        if lib.ftcuda_gemm_launch_scatter(byref(self.launch), c_void_p(workspace), workspace_bytes, pointers, len(owner_rows),
+                                          rows_per_owner, c_void_p(stream), buffer, 256) != 0:
             raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
 
 

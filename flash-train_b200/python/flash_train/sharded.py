@@ -166,13 +166,18 @@ class FusedKShardedGemm:
     every other rank's rows. A call: the owner writes beta * C (or zeros) into its rows; a barrier;
     every rank launches the tensor-core kernel on its K range through ftcuda_gemm_launch_scatter,
     whose epilogue adds alpha * (A_r B_r) into the owners' rows with FP32 atomics over NVLink; a
-    barrier; the rows are complete. No partial matrix, no reduce-scatter, no workspace. The order of
-    the additions is not fixed: results agree with the reduce-scatter form to rounding, not bitwise.
+    barrier; the rows are complete. No reduce-scatter. When the local kernel splits K (to even out its
+    waves) the slices are, by default, first summed on this GPU (a workspace, the library's reduction
+    kernel adding into the owners' rows), so that every element crosses NVLink once; with
+    local_combine=False every slice adds directly and nothing is stored at all. The order of the
+    additions is not fixed: results agree with the reduce-scatter form to rounding, not bitwise.
 
     Operands must suit the tensor-core kernels (16-byte aligned bases and pitches).
     """
 
-    def __init__(self, m: int, n: int, k: int, group=None, device=None):
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, local_combine: bool = True):
+        """local_combine: give the local split-K a workspace so that its K slices are summed on this GPU
+        and every element crosses NVLink once; False: no workspace, every slice adds directly."""
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symmetric_memory
@@ -195,6 +200,8 @@ class FusedKShardedGemm:
         self._handle = symmetric_memory.rendezvous(self.out, self.group)
         self._owner_rows = [int(self._handle.buffer_ptrs[r]) for r in range(self.world)]
         self._launches = {}
+        self._local_combine = local_combine
+        self._workspace = None
 
     def _launch_for(self, a_cols, b_rows, alpha: float):
         capi = self._capi
@@ -226,6 +233,11 @@ class FusedKShardedGemm:
         self._handle.barrier()  # every owner's rows are initialised before anybody adds to them
         if depth > 0:
             launch = self._launch_for(a_cols, b_rows, alpha)
-            launch.run_scatter(self._owner_rows, self.rows, torch.cuda.current_stream(self.device).cuda_stream)
+            workspace, size = 0, 0
+            if self._local_combine and launch.workspace_bytes > 0:
+                if self._workspace is None or self._workspace.numel() < launch.workspace_bytes:
+                    self._workspace = torch.empty(launch.workspace_bytes, dtype=torch.uint8, device=self.device)
+                workspace, size = self._workspace.data_ptr(), launch.workspace_bytes
+            launch.run_scatter(self._owner_rows, self.rows, torch.cuda.current_stream(self.device).cuda_stream, workspace, size)
         self._handle.barrier()  # every rank's additions have been issued and are complete
         return self.out

@@ -139,13 +139,17 @@ FTCUDA_API uint64_t ftcuda_gemm_splitk_static_capacity(void);
  * memory); the additions are single FP32 atomics travelling over NVLink. The
  * caller initialises every buffer (zeros, or beta * C) and orders that before
  * the launch, and the launches of all GPUs before the first read, with
- * barriers of its own. c and beta of the descriptor are ignored; no workspace
- * is needed even for the split-K family (its K slices add directly). The order
- * of the additions is not fixed, so the last bits of the result can differ
- * from run to run.
+ * barriers of its own. c and beta of the descriptor are ignored. The workspace
+ * is optional: without one (NULL, or fewer bytes than
+ * ftcuda_gemm_workspace_bytes) every K slice of the split-K family adds its
+ * tile directly, one launch, nothing stored; with one the slices are combined
+ * on this GPU first and every element crosses NVLink once (two launches). The
+ * order of the additions is not fixed, so the last bits of the result can
+ * differ from run to run.
  */
-FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, float* const* owner_rows, int32_t owners,
-                                          uint64_t rows_per_owner, void* stream, char* message, size_t message_capacity);
+FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                          float* const* owner_rows, int32_t owners, uint64_t rows_per_owner, void* stream,
+                                          char* message, size_t message_capacity);
 
 /* Number of device kernels ftcuda_gemm_launch has enqueued from this process;
  * benchmarks read it to report how many launches a timed region made. */

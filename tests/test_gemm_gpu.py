@@ -478,20 +478,25 @@ def test_scatter_launch_adds_rows_into_owner_buffers(capi, gpu, oracle, kernel):
     b = torch.randn(k, n, device="cuda")
     c = torch.randn(m, n, device="cuda")
     alpha, beta = 0.75, -1.25
-    blocks = [(beta * c[i * rows:(i + 1) * rows]).contiguous() for i in range(owners)]
-    for k_start, k_stop in ((0, 2304), (2304, 4608)):
-        a_cols = a[:, k_start:k_stop].contiguous()
-        b_rows = b[k_start:k_stop].contiguous()
-        unused = torch.empty(m, n, device="cuda")
-        desc = capi.make_desc(gpu.operand(a_cols), gpu.operand(b_rows), capi.null_operand(m, n), gpu.operand(unused), alpha, 0.0,
-                              torch.cuda.current_device())
-        reason = capi.platform_supports(kernel, desc)
-        if reason is not None:
-            pytest.skip(reason)
-        launch = capi.PlatformGemm(kernel, desc)
-        launch.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream())
-    torch.cuda.synchronize()
-    check_against_float64(oracle, torch.cat(blocks), a, b, c, alpha, beta, f"scatter launch, {capi.KERNEL_NAMES[kernel]}")
+    for with_workspace in (False, True):  # every K slice adds directly / slices combined locally first
+        blocks = [(beta * c[i * rows:(i + 1) * rows]).contiguous() for i in range(owners)]
+        for k_start, k_stop in ((0, 2304), (2304, 4608)):
+            a_cols = a[:, k_start:k_stop].contiguous()
+            b_rows = b[k_start:k_stop].contiguous()
+            unused = torch.empty(m, n, device="cuda")
+            desc = capi.make_desc(gpu.operand(a_cols), gpu.operand(b_rows), capi.null_operand(m, n), gpu.operand(unused), alpha, 0.0,
+                                  torch.cuda.current_device())
+            reason = capi.platform_supports(kernel, desc)
+            if reason is not None:
+                pytest.skip(reason)
+            launch = capi.PlatformGemm(kernel, desc)
+            size = launch.workspace_bytes if with_workspace else 0
+            workspace = torch.empty(max(size, 1), dtype=torch.uint8, device="cuda")
+            launch.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream(),
+                               workspace.data_ptr() if size else 0, size)
+        torch.cuda.synchronize()
+        check_against_float64(oracle, torch.cat(blocks), a, b, c, alpha, beta,
+                              f"scatter launch, {capi.KERNEL_NAMES[kernel]}, workspace={with_workspace}")
     # Argument checks: owners must cover m, buffers must exist, only tensor-core families scatter.
     with pytest.raises(capi.FTrainError, match="do not cover"):
         launch.run_scatter([blocks[0].data_ptr()], rows, gpu.current_stream())

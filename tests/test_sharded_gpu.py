@@ -49,13 +49,14 @@ def worker(rank, world, port, failures):
     # The same K-sharded product with the reduction fused into the kernel's epilogue: every rank adds
     # its results into the owners' rows through peer-mapped symmetric memory.
     try:
-        fused = sharded.FusedKShardedGemm(m, n, k)
-        for _ in range(2):  # the second call reuses the symmetric buffer
+        for local_combine in (True, False):
+          fused = sharded.FusedKShardedGemm(m, n, k, local_combine=local_combine)
+          for _ in range(2):  # the second call reuses the symmetric buffer
             d_fused = fused(a[:, fused.k_start:fused.k_stop].contiguous(), b[fused.k_start:fused.k_stop].contiguous(),
                             c[split.row_start:split.row_stop].contiguous(), 1.25, -0.5)
             torch.cuda.synchronize()
             if not torch.allclose(d_fused.double(), exact[split.row_start:split.row_stop], rtol=1e-4, atol=2e-2):
-                failures.append(f"rank {rank}: fused K-sharded result is off")
+                failures.append(f"rank {rank}: fused K-sharded result is off (local_combine={local_combine})")
     except Exception as error:  # noqa: BLE001 - reported to the parent, the process leaves in order
         failures.append(f"rank {rank}: fused K-sharded GEMM raised {type(error).__name__}: {error}")
     dist.barrier()
