@@ -413,7 +413,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // Number of K slices that fills the SMs in whole waves: the smallest count
 // whose last wave is at least 90 % full, bounded by the slice length.
 std::uint32_t chooseSplits(std::uint64_t tiles, std::uint64_t k, int sms) {
-    const std::uint64_t most = k / 1024 < 2 ? 2 : k / 1024;  // slices of >= 1024
+    const std::uint64_t most = k / 256 < 2 ? 2 : k / 256;  // slices of >= 256 (8 K blocks)
     std::uint32_t best       = 2;
     double best_fill         = 0.0;
     for (std::uint64_t s = 2; s <= most && s <= 128; ++s) {
@@ -483,7 +483,7 @@ const char* supportsTensor(const FtcudaGemmDesc& desc, bool split_k) {
         return "B is neither row-major nor a transposed row-major view with a 16-byte aligned base and pitch";
     }
     if (ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN) >= (1ULL << 24)) { return "too many output tiles"; }
-    if (split_k && desc.k < 2048) { return "K is too short to split"; }
+    if (split_k && desc.k < 512) { return "K is too short to split"; }
     return nullptr;
 }
 

@@ -24,8 +24,8 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 //     the 128x192 tiles fill less than 90 % of the SMs' waves and K >= 2048,
 //     the split-K variant (workspace needed) goes first so that K slices even
 //     out the waves; the unsplit kernels follow for callers without workspace.
-//     Under 128 rows with a medium K (512 ... 2047) and few tiles, the exact
-//     split-K SIMT kernel is the fastest.
+//     With a medium K (512 ... 2047) the split pays only while the tiles fill
+//     under half a wave (the partial sums stay small).
 //   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
 //     leave most SMs idle and K >= 512.
 // Every list ends with "Fp32Gemm", which needs no workspace and accepts every
@@ -50,8 +50,9 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const std::uint64_t few_ctas   = ceilDiv(shape.n, strip) * 8;  // CTAs the few-rows kernel can start
         // The more rows, the more arithmetic per CTA (from 17 rows on the kernel is
         // bound by the FP32 pipe and runs one CTA per SM), the more CTAs it needs.
+        // Beyond 24 rows the tensor cores win whatever the width.
         const bool narrow = few_ctas * 4 <= sm_count || (few_ctas * 2 <= sm_count && shape.m > 8) ||
-                            (few_ctas <= sm_count && shape.m > 16);
+                            (few_ctas <= sm_count && shape.m > 16) || shape.m > 24;
         if (narrow && shape.k >= 2048) { return {tensor_split, skinny, simt_split, simt}; }
         return {skinny, simt_split, simt};
     }
@@ -62,7 +63,9 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
         const bool ragged         = tiles * 10 < waves * sm_count * 9;  // the waves are under 90 % full overall
         if (ragged && shape.k >= 2048) { return {tensor_split, tensor, simt_split, simt}; }
-        if (shape.m < 128 && shape.k >= 512 && simt_tiles * 2 <= sm_count) { return {simt_split, tensor, simt}; }
+        // A medium K is worth cutting only while the output (the partial sums the
+        // second pass re-reads) is small: under half a wave of tiles.
+        if (shape.k >= 512 && tiles * 2 <= sm_count) { return {tensor_split, tensor, simt_split, simt}; }
         return {tensor, simt};
     }
     if (simt_tiles * 2 <= sm_count && shape.k >= 512) { return {simt_split, simt}; }

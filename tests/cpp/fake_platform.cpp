@@ -55,7 +55,7 @@ extern "C" int ftcuda_gemm_supports(int kernel, const FtcudaGemmDesc* desc, char
             if (desc->m * desc->n == 0 || desc->k < 32) { return fake::fail(message, capacity, "K is shorter than one K block"); }
             if (!row_major_a) { return fake::fail(message, capacity, "A is not row-major with a 16-byte aligned base and row pitch"); }
             if (!row_major_b) { return fake::fail(message, capacity, "B is not row-major with a 16-byte aligned base and row pitch"); }
-            if (kernel == FTCUDA_GEMM_TF32X3_SPLITK && desc->k < 2048) { return fake::fail(message, capacity, "K is too short to split"); }
+            if (kernel == FTCUDA_GEMM_TF32X3_SPLITK && desc->k < 512) { return fake::fail(message, capacity, "K is too short to split"); }
             return 0;
         case FTCUDA_GEMM_SKINNY:
             if (desc->m == 0 || desc->m > 32) { return fake::fail(message, capacity, "more than 32 rows (or none) in A"); }

@@ -245,7 +245,8 @@ TEST(finder_regime_map) {
     // From 33 rows on the tensor kernel's 128-row tile wins over the SIMT kernel.
     CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(64, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
-    CHECK(first(64, 1024, 1024) == (Names{"Fp32GemmSplitK", "Fp32Gemm3xTf32", "Fp32Gemm"}));
+    CHECK(first(64, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
+    CHECK(first(1024, 1024, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // Few rows but a narrow B: too few strips for the few-rows kernel.
     CHECK(first(17, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
@@ -253,7 +254,8 @@ TEST(finder_regime_map) {
     CHECK(first(8, 16384, 1024).front() == "Fp32GemmSkinny");
     CHECK(first(32, 4096, 2048).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(16, 4096, 2048).front() == "Fp32GemmSkinny");
-    CHECK(first(32, 4096, 4096).front() == "Fp32GemmSkinny");
+    CHECK(first(32, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(24, 4096, 4096).front() == "Fp32GemmSkinny");
     CHECK(first(64, 1024, 64) == (Names{"Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(16384, 4096, 14336) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(2048, 262144, 2048) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
