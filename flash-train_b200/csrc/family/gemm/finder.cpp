@@ -25,7 +25,7 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 //     the split-K variant (workspace needed) goes first so that K slices even
 //     out the waves; the unsplit kernels follow for callers without workspace.
 //     With a medium K (512 ... 2047) the split pays only while the tiles fill
-//     under half a wave (the partial sums stay small).
+//     under a quarter of a wave (two launches; the partial sums stay small).
 //   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
 //     leave most SMs idle and K >= 512.
 // Every list ends with "Fp32Gemm", which needs no workspace and accepts every
@@ -63,9 +63,9 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
         const bool ragged         = tiles * 10 < waves * sm_count * 9;  // the waves are under 90 % full overall
         if (ragged && shape.k >= 2048) { return {tensor_split, tensor, simt_split, simt}; }
-        // A medium K is worth cutting only while the output (the partial sums the
-        // second pass re-reads) is small: under half a wave of tiles.
-        if (shape.k >= 512 && tiles * 2 <= sm_count) { return {tensor_split, tensor, simt_split, simt}; }
+        // A medium K is worth cutting (two launches, partial sums re-read by the
+        // second) only while the tiles fill under a quarter of a wave.
+        if (shape.k >= 512 && tiles * 4 <= sm_count) { return {tensor_split, tensor, simt_split, simt}; }
         return {tensor, simt};
     }
     if (simt_tiles * 2 <= sm_count && shape.k >= 512) { return {simt_split, simt}; }

@@ -247,6 +247,7 @@ TEST(finder_regime_map) {
     CHECK(first(64, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(64, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    CHECK(first(1024, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // Few rows but a narrow B: too few strips for the few-rows kernel.
     CHECK(first(17, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
