@@ -69,8 +69,8 @@ DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on one GPU, from the ncu
 # captures summarised under profiles/ (a benchmark run cannot profile itself).
 MEASURED_DRAM_TRAFFIC = {
-    ("gemm_fp32_16384x4096x14336", "Fp32Gemm3xTf32", 1): 3241293312 + 927234304,
-    ("gemm_fp32_4096x4096x4096_addend", "Fp32Gemm3xTf32", 1): 383589120 + 55749888,
+    ("gemm_fp32_16384x4096x14336", "Fp32Gemm3xTf32", 1): 3226008832 + 925021952,
+    ("gemm_fp32_4096x4096x4096_addend", "Fp32Gemm3xTf32", 1): 382524160 + 56027136,
     ("gemm_fp32_1x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67142912 + 49920,
     ("gemm_fp32_8x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67261184 + 69888,
     ("gemm_fp32_17x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67419392 + 43520,
