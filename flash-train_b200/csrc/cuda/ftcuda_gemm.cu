@@ -19,6 +19,7 @@ const char* supports(int kernel, const FtcudaGemmDesc& desc) {
         case FTCUDA_GEMM_TF32X3: return ftcuda::supportsTensor(desc, false);
         case FTCUDA_GEMM_TF32X3_SPLITK: return ftcuda::supportsTensor(desc, true);
         case FTCUDA_GEMM_SKINNY: return ftcuda::supportsSkinny(desc);
+        case FTCUDA_GEMM_TF32X3_ROWS: return ftcuda::supportsTensorRows(desc);
         default: return "unknown kernel family";
     }
 }
@@ -46,6 +47,7 @@ extern "C" int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, Ftc
         case FTCUDA_GEMM_SIMT_SPLITK: return ftcuda::configureSimt(state, true, message, message_capacity);
         case FTCUDA_GEMM_TF32X3: return ftcuda::configureTensor(state, false, message, message_capacity);
         case FTCUDA_GEMM_TF32X3_SPLITK: return ftcuda::configureTensor(state, true, message, message_capacity);
+        case FTCUDA_GEMM_TF32X3_ROWS: return ftcuda::configureTensorRows(state, message, message_capacity);
         default: return ftcuda::configureSkinny(state, message, message_capacity);
     }
 }
@@ -76,6 +78,7 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
         case FTCUDA_GEMM_TF32X3:
         case FTCUDA_GEMM_TF32X3_SPLITK: error = ftcuda::launchTensor(state, workspace, cuda_stream); break;
         case FTCUDA_GEMM_SKINNY: error = ftcuda::launchSkinny(state, cuda_stream); break;
+        case FTCUDA_GEMM_TF32X3_ROWS: error = ftcuda::launchTensorRows(state, cuda_stream); break;
         default: return ftcuda::fail(message, message_capacity, 1, "unknown kernel family %d", state.kernel);
     }
     if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }

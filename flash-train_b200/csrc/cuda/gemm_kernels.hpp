@@ -89,6 +89,11 @@ int configureTensorPair(LaunchState& state, char* message, std::size_t capacity)
 cudaError_t launchTensorPair(const LaunchState& state, const tf32x3::TensorParams& p, std::uint32_t items,
                              cudaStream_t stream);
 
+// 3xTF32 for few rows of A with the operands' roles swapped (gemm_tf32x3_rows.cu).
+const char* supportsTensorRows(const FtcudaGemmDesc& desc);
+int configureTensorRows(LaunchState& state, char* message, std::size_t capacity);
+cudaError_t launchTensorRows(const LaunchState& state, cudaStream_t stream);
+
 const char* supportsSimt(const FtcudaGemmDesc& desc, bool split_k);
 int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t capacity);
 cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream);

@@ -446,9 +446,7 @@ std::uint32_t chunkKBlocks(std::uint64_t k) {
         const long value = std::strtol(text, nullptr, 10);
         if (value >= 1 && value <= (1L << 20)) { return static_cast<std::uint32_t>(value); }
     }
-    std::uint32_t blocks = 1;
-    while (blocks < 16 && static_cast<std::uint64_t>(blocks + 1) * (blocks + 1) * 156 <= k) { ++blocks; }  // 12.5^2 = 156.25
-    return blocks;
+    return drainInterval(k);
 }
 
 // Output tiles are walked in bands of this many M tiles (all N tiles of a band

@@ -13,6 +13,14 @@ namespace tf32x3 {
 constexpr int kTileN = 192;
 constexpr int kTileK = 32;
 
+// K blocks (of 32) accumulated inside the tensor core between two drains, by default: floor(sqrt(K) / 12.5)
+// clamped to [1, 16] (see chunkKBlocks in gemm_tf32x3.cu for the measurements behind it).
+inline std::uint32_t drainInterval(std::uint64_t k) {
+    std::uint32_t blocks = 1;
+    while (blocks < 16 && static_cast<std::uint64_t>(blocks + 1) * (blocks + 1) * 156 <= k) { ++blocks; }  // 12.5^2 = 156.25
+    return blocks;
+}
+
 struct TensorParams {
     const float* c;
     float* d;

@@ -29,6 +29,7 @@ std::vector<std::shared_ptr<const Primitive<GemmProblem>>> GemmFamily::makeRecor
         std::make_shared<CudaGemm>(FTCUDA_GEMM_SKINNY),
         std::make_shared<CudaGemm>(FTCUDA_GEMM_TF32X3_SPLITK),
         std::make_shared<CudaGemm>(FTCUDA_GEMM_SIMT_SPLITK),
+        std::make_shared<CudaGemm>(FTCUDA_GEMM_TF32X3_ROWS),
     };
 }
 

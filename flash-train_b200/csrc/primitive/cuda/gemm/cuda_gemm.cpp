@@ -22,6 +22,7 @@ const char* cudaGemmName(int kernel) noexcept {
         case FTCUDA_GEMM_TF32X3_SPLITK: return "Fp32Gemm3xTf32SplitK";
         case FTCUDA_GEMM_SKINNY: return "Fp32GemmSkinny";
         case FTCUDA_GEMM_SIMT_SPLITK: return "Fp32GemmSplitK";
+        case FTCUDA_GEMM_TF32X3_ROWS: return "Fp32Gemm3xTf32FewRows";
         default: return nullptr;
     }
 }

@@ -360,9 +360,11 @@ KERNEL_TF32X3 = 1
 KERNEL_TF32X3_SPLITK = 2
 KERNEL_SKINNY = 3
 KERNEL_SIMT_SPLITK = 4
+KERNEL_TF32X3_ROWS = 5
 KERNEL_NAMES = {
     KERNEL_SIMT: "Fp32Gemm",
     KERNEL_TF32X3: "Fp32Gemm3xTf32",
+    KERNEL_TF32X3_ROWS: "Fp32Gemm3xTf32FewRows",
     KERNEL_TF32X3_SPLITK: "Fp32Gemm3xTf32SplitK",
     KERNEL_SKINNY: "Fp32GemmSkinny",
     KERNEL_SIMT_SPLITK: "Fp32GemmSplitK",

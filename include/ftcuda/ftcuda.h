@@ -47,7 +47,10 @@ enum {
     FTCUDA_GEMM_SKINNY = 3,
     /* Exact FP32 SIMT with the K range split across CTAs (workspace). */
     FTCUDA_GEMM_SIMT_SPLITK = 4,
-    FTCUDA_GEMM_KERNEL_COUNT = 5,
+    /* 3xTF32 for few rows of A (m <= 64): B fills the tensor core's 128-row
+     * dimension (D^T = B^T A^T), K split over a thread-block cluster. No workspace. */
+    FTCUDA_GEMM_TF32X3_ROWS = 5,
+    FTCUDA_GEMM_KERNEL_COUNT = 6,
 };
 
 /* One GEMM D = alpha * A * B + beta * C in terms of raw memory. Strides are in

@@ -61,6 +61,10 @@ extern "C" int ftcuda_gemm_supports(int kernel, const FtcudaGemmDesc* desc, char
             if (desc->m == 0 || desc->m > 32) { return fake::fail(message, capacity, "more than 32 rows (or none) in A"); }
             if (desc->n % 4 != 0 || !row_major_b) { return fake::fail(message, capacity, "B is not row-major with a 16-byte row pitch"); }
             return 0;
+        case FTCUDA_GEMM_TF32X3_ROWS:
+            if (desc->m == 0 || desc->m > 64) { return fake::fail(message, capacity, "more than 64 rows (or none) in A"); }
+            if (desc->k < 128 || !row_major_a || !row_major_b) { return fake::fail(message, capacity, "layout or K unsuitable"); }
+            return 0;
         default: return fake::fail(message, capacity, "unknown kernel family");
     }
 }

@@ -289,6 +289,6 @@ TEST(builtin_gemm_engine_is_registered) {
     CHECK(handle.findOpsEngine(PatternBuilder().build().getKey()) == nullptr);
     CHECK_THROWS_STATUS(handle.registerOpsEngine(nullptr), FTRAIN_STATUS_INVALID_ARGUMENT);
     CHECK_THROWS_STATUS(handle.registerOpsEngine(makeBuiltinOpsEngines().front()), FTRAIN_STATUS_INVALID_ARGUMENT);
-    CHECK_EQ(GemmFamily::makeRecords().size(), static_cast<std::size_t>(5));
+    CHECK_EQ(GemmFamily::makeRecords().size(), static_cast<std::size_t>(6));
     CHECK_EQ(std::string(GemmFamily::makeRecords().front()->getName()), std::string("Fp32Gemm"));
 }

@@ -99,7 +99,7 @@ def test_reference_grid_selected_primitive(capi, gpu, oracle, shape):
     assert ok, f"accumulated {names[0]}: worst ratio {ratio}"
 
 
-@pytest.mark.parametrize("kernel", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("kernel", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("shape", GRID + [(128, 64, 96), (255, 512, 260), (17, 2304, 64), (384, 4100, 516)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_every_kernel_family_against_oracle(capi, gpu, oracle, kernel, shape):
@@ -534,7 +534,8 @@ def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle
                 continue
             ran[name] += 1
             what = f"case {case}: {name} {m}x{k}x{n} a_t={a_t} b_t={b_t} pads=({pad_a},{pad_b}) alpha={alpha} beta={beta}"
-            if k <= 300 or kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK, capi.KERNEL_SKINNY, capi.KERNEL_SIMT_SPLITK):
+            if k <= 300 or kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK, capi.KERNEL_TF32X3_ROWS, capi.KERNEL_SKINNY,
+                                      capi.KERNEL_SIMT_SPLITK):
                 # Blocked sums (or short K): the float64 bar applies as it stands.
                 check_against_float64(oracle, d, a.contiguous(), b.contiguous(), c, alpha, beta, what)
             else:
@@ -545,3 +546,37 @@ def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle
                 assert ((d.double() - exact).abs() <= slack * (1.0 + scale)).all(), what
     # The draw must actually have exercised every family.
     assert all(count >= 5 for count in ran.values()), ran
+
+
+@pytest.mark.parametrize("m", [1, 9, 16, 17, 32, 33, 64])
+def test_tensor_few_rows_kernel(capi, gpu, oracle, m):
+    """The 3xTF32 kernel with B as the tensor core's 128-row operand: every padded row count (16, 32,
+    64), n off the 128-column strip, K off the K block and long enough for several drains and for the
+    cluster to split it, B wider than n, with and without C."""
+    import os
+
+    if os.environ.get("FT_SKIP_TENSOR"):
+        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
+    torch.manual_seed(200 + m)
+    for k, n, pitch in ((1000, 200, 200), (4096 + 36, 130, 132), (8192, 4096, 4096), (260, 517, 520), (16384, 1024, 1024)):
+        a = torch.randn(m, k, device="cuda")
+        b = torch.randn(k, pitch, device="cuda")[:, :n]
+        c = torch.randn(m, n, device="cuda")
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, a, b, c, 1.5, -0.25)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, b.contiguous(), c, 1.5, -0.25, f"tensor few rows m={m} k={k} n={n}")
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, a, b, None, 1.0, 0.0)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, b.contiguous(), None, 1.0, 0.0, f"tensor few rows, no C, m={m} k={k} n={n}")
+        # B handed over as the transposed view of an [n][k] matrix (x @ W.T): its strip tile is a K-major operand.
+        bt = torch.randn(n, k + 4, device="cuda")[:, :k].t()
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, a, bt, c, 1.5, -0.25)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, bt.contiguous(), c, 1.5, -0.25, f"tensor few rows, B along K, m={m} k={k} n={n}")
+    # Declined: too many rows, A stored by columns, short K.
+    wide = torch.randn(65, 512, device="cuda")
+    assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, wide, torch.randn(512, 256, device="cuda"), None, 1.0, 0.0)[0] is None
+    assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, torch.randn(512, 8, device="cuda").t(),
+                         torch.randn(512, 256, device="cuda"), None, 1.0, 0.0)[0] is None
+    assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, torch.randn(8, 64, device="cuda"), torch.randn(64, 256, device="cuda"),
+                         None, 1.0, 0.0)[0] is None
