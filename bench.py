@@ -22,7 +22,7 @@ host. The call moves A, C and D in bands of rows so that copy-in, kernels and
 copy-out of successive bands overlap; all of it is inside the timed region.
 
 Other workloads (--workload): the 4096^3 GEMM with addend; the default shape with B as a transposed view
-(`_bt`); the few-rows shapes m = 1 / 8 / 17 with k = n = 4096 (`_fewrows`, HBM-bound, B rotating over four
+(`_bt`); the few-rows shapes m = 1 / 8 / 17 / 32 / 64 with k = n = 4096 (`_fewrows`, HBM-bound, B rotating over four
 matrices; `_fewrows_bt` with B as the transposed view of a weight matrix); the tall-K GEMM sharded along K
 over the GPUs, reduced by NCCL reduce-scatter (`_ksplit`) or inside the kernel's epilogue over peer memory
 (`_ksplit_fused`); and `finder_sweep`, which times every kernel family on a grid of shapes against the
@@ -61,9 +61,12 @@ KSPLIT_FUSED_WORKLOAD = KSPLIT_WORKLOAD + "_fused"  # the reduction inside the k
 KSPLIT_SHAPE = (2048, 262144, 2048)
 # Few-rows (memory-bound) shapes of the tail sweep, k = n = 4096, entries U(-1, 1): one GPU streams B once.
 FEW_ROWS_WORKLOADS = {"gemm_fp32_1x4096x4096_fewrows": 1, "gemm_fp32_8x4096x4096_fewrows": 8,
-                      "gemm_fp32_17x4096x4096_fewrows": 17,
+                      "gemm_fp32_17x4096x4096_fewrows": 17, "gemm_fp32_32x4096x4096_fewrows": 32,
+                      "gemm_fp32_64x4096x4096_fewrows": 64,
                       # B as the transposed view of an n x k weight matrix (x @ W^T)
                       "gemm_fp32_1x4096x4096_fewrows_bt": 1, "gemm_fp32_8x4096x4096_fewrows_bt": 8}
+FEW_ROWS_KERNELS = {"Fp32GemmSkinny": "skinnyGemm", "Fp32Gemm3xTf32FewRows": "tensorGemm3xTf32Rows",
+                    "Fp32Gemm3xTf32SplitK": "tensorGemm3xTf32 + splitKReduce"}
 FEW_ROWS_COPIES = 4  # distinct B matrices visited in turn: 4 x 64 MiB is twice the 126 MB L2
 DEFAULT_WORKLOAD = "gemm_fp32_16384x4096x14336"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on one GPU, from the ncu
@@ -74,6 +77,8 @@ MEASURED_DRAM_TRAFFIC = {
     ("gemm_fp32_1x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67142912 + 49920,
     ("gemm_fp32_8x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67261184 + 69888,
     ("gemm_fp32_17x4096x4096_fewrows", "Fp32GemmSkinny", 1): 67419392 + 43520,
+    # dram__bytes.sum.per_second x gpu__time_duration.sum of one launch (reads and writes together)
+    ("gemm_fp32_32x4096x4096_fewrows", "Fp32Gemm3xTf32FewRows", 1): 68317000,
 }
 CPU_SAMPLE_ROWS = 2048  # rows of A per CPU-baseline step
 
@@ -328,9 +333,9 @@ def torch_gemm_overhead(ft_torch, torch, device) -> dict:
 
 SWEEP_WORKLOAD = "finder_sweep"
 # (m, k, n, B given as the transposed view of an n x k buffer)
-SWEEP_SHAPES = [(m, k, n, False) for (k, n) in ((4096, 4096), (1024, 1024), (256, 4096), (16384, 1024), (65536, 512))
-                for m in (1, 8, 17, 32, 33, 64, 128, 256, 1024, 4097)] + \
-               [(m, k, n, True) for (k, n) in ((4096, 4096), (16384, 1024), (65536, 512)) for m in (1, 8, 32, 64, 256, 4097)]
+SWEEP_SHAPES = [(m, k, n, False) for (k, n) in ((4096, 4096), (2048, 2048), (1024, 1024), (256, 4096), (16384, 1024), (65536, 512))
+                for m in (1, 8, 12, 16, 17, 32, 33, 64, 128, 256, 1024, 4097)] + \
+               [(m, k, n, True) for (k, n) in ((4096, 4096), (16384, 1024), (65536, 512)) for m in (1, 8, 16, 32, 64, 256, 4097)]
 
 
 def run_finder_sweep(options, torch, capi, rank, device) -> int:
@@ -379,8 +384,9 @@ def run_finder_sweep(options, torch, capi, rank, device) -> int:
 
 
 def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
-    """m in {1, 8, 17}, k = n = 4096: the selected Primitive is the few-rows kernel and the step is
-    HBM-bound (B is read once). Every rank runs the same problem on its own GPU (replicas)."""
+    """m in {1, 8, 17, 32, 64}, k = n = 4096: the selected Primitive is a few-rows kernel (the exact one up
+    to 11 rows, the 3xTF32 one with B as the tensor core's 128-row operand from 12 rows on) and the step's
+    floor is reading B once from HBM. Every rank runs the same problem on its own GPU (replicas)."""
     from flash_train.capi import GemmBinding, null_operand, tensor_operand
 
     m, k, n = FEW_ROWS_WORKLOADS[options.workload], 4096, 4096
@@ -447,7 +453,7 @@ def run_few_rows(options, torch, capi, world, rank, local_rank, device) -> int:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "traffic": MEASURED_DRAM_TRAFFIC.get((options.workload, primitive, 1)),
                          "algorithmic_bytes": algorithmic, "peak_source": f"{peaks['source']} hbm_gbs (copy)",
-                         "kernel": "skinnyGemm", "us_per_launch": ms_per_gemm * 1e3},
+                         "kernel": FEW_ROWS_KERNELS.get(primitive, primitive), "us_per_launch": ms_per_gemm * 1e3},
             "clocks": clocks, "gpu_launches": launches,
         }
         print(json.dumps(line), flush=True)

@@ -230,8 +230,11 @@ skinnyGemm(const __grid_constant__ CUtensorMap map_b, const SkinnyParams p) {
                 float4 b_value[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) { b_value[r] = *reinterpret_cast<const float4*>(rows + r * (kStripColumns * 4)); }
+                // The box is in registers now. The proxy fence orders these generic-proxy reads before
+                // the TMA write that refills the slot.
+                fenceProxyAsync();
                 __syncwarp();
-                if (lane == 0) { mbarrierArrive(&empty[s]); }  // the box is in registers now
+                if (lane == 0) { mbarrierArrive(&empty[s]); }
                 if (warp == 0 && box >= 1 && issued < boxes) {
                     const std::uint32_t freed = box - 1;  // its slot takes box freed + kSlots == issued
                     if (!__all_sync(0xFFFFFFFFU, mbarrierWait(&empty[freed % kSlots], (freed / kSlots) & 1, &abort_flag))) {
@@ -460,6 +463,7 @@ skinnyGemmBt(const __grid_constant__ CUtensorMap map_b, const SkinnyParams p) {
         float4 b_value[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) { b_value[r] = *reinterpret_cast<const float4*>(rows + r * (kBtBoxK * 4)); }
+        fenceProxyAsync();  // reads of the slot before its refill by TMA
         __syncwarp();
         if (lane == 0) { mbarrierArrive(&empty[s]); }
         if (warp == 0 && box >= 1 && issued < boxes) {

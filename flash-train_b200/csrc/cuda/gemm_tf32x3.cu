@@ -325,14 +325,16 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
                     }
                 }
-                __syncwarp();
-                if (lane == 0) { mbarrierArrive(&bars->raw_empty[r]); }
                 // Publish: shared-memory writes to the async proxy, tensor-memory
-                // stores (already waited for) to the MMA issuer.
+                // stores (already waited for) to the MMA issuer. The same proxy fence
+                // orders this warp's reads of the raw slot before its refill by TMA.
                 fenceProxyAsync();
                 tcgen05FenceBeforeSync();
                 __syncwarp();
-                if (lane == 0) { mbarrierArrive(&bars->conv_done[s]); }
+                if (lane == 0) {
+                    mbarrierArrive(&bars->raw_empty[r]);
+                    mbarrierArrive(&bars->conv_done[s]);
+                }
             }
         }
         if (!ok) { *abort_flag = 1; }

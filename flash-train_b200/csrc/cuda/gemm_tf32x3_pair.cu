@@ -306,14 +306,16 @@ tensorGemm3xTf32Pair(const __grid_constant__ CUtensorMap map_a, const __grid_con
                         *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
                     }
                 }
-                __syncwarp();
-                if (lane == 0) { mbarrierArrive(&bars->raw_empty[r]); }
                 // Publish: shared-memory writes to the async proxy, tensor-memory
-                // stores (already waited for) to the MMA issuer in the even CTA.
+                // stores (already waited for) to the MMA issuer in the even CTA. The same
+                // proxy fence orders this warp's reads of the raw slot before its refill by TMA.
                 fenceProxyAsync();
                 tcgen05FenceBeforeSync();
                 __syncwarp();
-                if (lane == 0) { mbarrierArriveInCta(&bars->conv_done[s], 0); }
+                if (lane == 0) {
+                    mbarrierArrive(&bars->raw_empty[r]);
+                    mbarrierArriveInCta(&bars->conv_done[s], 0);
+                }
             }
         }
         if (!ok) { *abort_flag = 1; }

@@ -143,11 +143,9 @@ struct Barriers {
 __device__ __forceinline__ void clusterArrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void clusterWait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
-// Splits `bytes` (a multiple of 512) at `raw` into hi and lo copies at the same offsets.
 // A converter warp's share of a raw tile, kBytes from `raw`, already split into TF32 hi and lo parts:
 // lane L holds bytes [512 i + 16 L, +16) of pass i. All loads are issued before the first value is
-// used (a converter's time per K block is latency, not arithmetic), and every value has been used by
-// the time load() returns: the raw slot may be handed back then.
+// used: a converter's time per K block is latency, not arithmetic.
 template<int kBytes>
 struct SplitShare {
     static constexpr int kPasses = (kBytes + 511) / 512;
@@ -348,23 +346,23 @@ tensorGemm3xTf32Rows(const __grid_constant__ CUtensorMap map_a, const __grid_con
             unsigned char* stage      = smem + kStageOffset + s * kStageBytes;
             ok = mbarrierWait(&bars->raw_full[r], (kb / kRawSlots) & 1, abort_flag);
             if (!ok) { break; }
-            // Split in registers; the slot can then be refilled while this warp still waits for the
-            // converted stage to come free. The fence makes the loads complete before the slot is handed
-            // back: with the loads merely issued, the refill was seen to overtake them.
+            // Load and split in registers while the converted stage may still be busy. The raw slot is
+            // handed back only below, behind the proxy fence: released right after the loads (even
+            // behind a block-level fence) a refill by TMA was seen to overtake them now and then.
             SplitShare<kBShare> b_parts;
             SplitShare<kAShare> a_parts;
             b_parts.load(slot + b_at, lane);
             a_parts.load(slot + kRawBBytes + a_at, lane);
-            __threadfence_block();
-            __syncwarp();
-            if (lane == 0) { mbarrierArrive(&bars->raw_empty[r]); }
             ok = mbarrierWait(&bars->mma_done[s], stage_parity ^ 1, abort_flag);
             if (!ok) { break; }
             b_parts.store(stage + b_at, stage + kRawBBytes + b_at, lane);
             a_parts.store(stage + 2 * kRawBBytes + a_at, stage + 2 * kRawBBytes + kRawABytes + a_at, lane);
             fenceProxyAsync();
             __syncwarp();
-            if (lane == 0) { mbarrierArrive(&bars->conv_done[s]); }
+            if (lane == 0) {
+                mbarrierArrive(&bars->raw_empty[r]);
+                mbarrierArrive(&bars->conv_done[s]);
+            }
             if (++s == kStages) {
                 s = 0;
                 stage_parity ^= 1;

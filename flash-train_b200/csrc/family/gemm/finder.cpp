@@ -43,9 +43,33 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     const char* skinny       = cudaGemmName(FTCUDA_GEMM_SKINNY);
     const char* simt_split   = cudaGemmName(FTCUDA_GEMM_SIMT_SPLITK);
 
+    const char* tensor_rows  = cudaGemmName(FTCUDA_GEMM_TF32X3_ROWS);
+
     if (shape.m * shape.n == 0) { return {simt}; }
+    const bool b_along_k = problem.getLayout(GemmPort::kB).row_stride == 1 && shape.n > 1;
+    // The tensor few-rows kernel (B as the tensor core's 128-row operand): one CTA per 128-column
+    // strip and K slice, at most eight slices. Measured against the other families on B200:
+    // it wins from 12 rows on for large B (from 17 rows whatever the size, K >= 1024), and up
+    // to 64 rows, except where a narrow, deep problem leaves it too few CTAs: then the
+    // split-K tensor kernel, which cuts K as finely as it likes, comes first.
+    if (shape.m >= 12 && shape.m <= 64 && shape.n >= 128 && shape.k >= 256) {
+        const std::uint64_t strips = ceilDiv(shape.n, 128);
+        bool rows_first            = false;
+        bool deep                  = false;  // too deep for eight K slices per strip
+        if (shape.m <= 16) {
+            rows_first = shape.k >= 1024 && shape.k * shape.n >= (8ULL << 20) && (!b_along_k || strips >= 32);
+            deep       = strips * 16 <= sm_count && shape.k >= 16384;
+        } else if (shape.m <= 32) {
+            rows_first = shape.k >= 2048 || (shape.k >= 1024 && strips >= 32);
+            deep       = strips * 16 <= sm_count && shape.k >= 16384;
+        } else {
+            rows_first = true;
+            deep       = strips * 8 <= sm_count && shape.k >= 4096;
+        }
+        if (deep && (rows_first || shape.k >= 32768)) { return {tensor_split, tensor_rows, skinny, tensor, simt_split, simt}; }
+        if (rows_first) { return {tensor_rows, tensor_split, skinny, tensor, simt_split, simt}; }
+    }
     if (shape.m <= 32 && shape.k >= 256) {
-        const bool b_along_k           = problem.getLayout(GemmPort::kB).row_stride == 1 && shape.n > 1;
         const std::uint64_t strip      = b_along_k ? 32 : 128;
         const std::uint64_t few_ctas   = ceilDiv(shape.n, strip) * 8;  // CTAs the few-rows kernel can start
         // The more rows, the more arithmetic per CTA (from 17 rows on the kernel is

@@ -238,14 +238,29 @@ TEST(finder_regime_map) {
     };
     using Names = std::vector<std::string>;
     CHECK(first(1, 4096, 4096) == (Names{"Fp32GemmSkinny", "Fp32GemmSplitK", "Fp32Gemm"}));
-    CHECK(first(17, 4096, 4096).front() == "Fp32GemmSkinny");
+    // From 12 rows on (17 whatever the size of B) B goes through the tensor cores as their 128-row operand.
+    CHECK(first(17, 4096, 4096) == (Names{"Fp32Gemm3xTf32FewRows", "Fp32Gemm3xTf32SplitK", "Fp32GemmSkinny", "Fp32Gemm3xTf32",
+                                          "Fp32GemmSplitK", "Fp32Gemm"}));
+    CHECK(first(12, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(12, 2048, 2048).front() == "Fp32GemmSkinny");
+    CHECK(first(11, 4096, 4096).front() == "Fp32GemmSkinny");
+    CHECK(first(17, 512, 4096).front() == "Fp32GemmSkinny");
     // 2 x 22 tiles on 148 SMs and K long enough to cut: K slices first.
     CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(4097, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // From 33 rows on the tensor kernel's 128-row tile wins over the SIMT kernel.
-    CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(64, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
-    CHECK(first(64, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
+    CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(65, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    // Narrow and deep: eight K slices per strip are too few CTAs.
+    CHECK(first(64, 8192, 1024).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(64, 8192, 1024)[1] == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(48, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(64, 256, 4096).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(65, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    CHECK(first(17, 1024, 1024).front() == "Fp32GemmSkinny");
+    CHECK(first(17, 2048, 512).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(64, 1024, 1024).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(96, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // Few rows but a narrow B: too few strips for the few-rows kernel.
@@ -253,10 +268,10 @@ TEST(finder_regime_map) {
     CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(17, 16384, 1024).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(8, 16384, 1024).front() == "Fp32GemmSkinny");
-    CHECK(first(32, 4096, 2048).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(16, 4096, 2048).front() == "Fp32GemmSkinny");
-    CHECK(first(32, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(24, 4096, 4096).front() == "Fp32GemmSkinny");
+    CHECK(first(32, 4096, 2048).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(16, 4096, 2048).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(32, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(24, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(64, 1024, 64) == (Names{"Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(16384, 4096, 14336) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(2048, 262144, 2048) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));

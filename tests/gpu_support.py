@@ -6,7 +6,8 @@ import torch
 
 from flash_train import capi
 
-ALL_PRIMITIVES = ("Fp32Gemm", "Fp32Gemm3xTf32", "Fp32GemmSkinny", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK")
+ALL_PRIMITIVES = ("Fp32Gemm", "Fp32Gemm3xTf32", "Fp32GemmSkinny", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK",
+                  "Fp32Gemm3xTf32FewRows")
 EXACT_PRIMITIVES = ("Fp32Gemm", "Fp32GemmSkinny", "Fp32GemmSplitK")
 
 _binding = None

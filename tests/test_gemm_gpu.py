@@ -280,7 +280,7 @@ def test_config3_tail_sweep_contiguous_and_transposed(capi, gpu, oracle, m):
         # A second Plan for the same description reproduces the selection.
         assert gpu.make_plan(a_view, b, None, d).primitive_names() == names
     if m <= 17:
-        assert gpu.make_plan(a, b, None, d).primitive_name(0) == "Fp32GemmSkinny"
+        assert gpu.make_plan(a, b, None, d).primitive_name(0) == ("Fp32GemmSkinny" if m == 1 else "Fp32Gemm3xTf32FewRows")
     # The one-shot call takes no workspace here and must still succeed.
     once = torch.empty(m, n, device="cuda")
     capi.gemm_once(gpu.operand(a), gpu.operand(b), capi.null_operand(m, n), gpu.operand(once), 1.0, 0.0,
@@ -455,11 +455,11 @@ def test_few_rows_kernel_with_b_contiguous_along_k(capi, gpu, oracle, m):
         assert d is not None, reason
         check_against_float64(oracle, d, a_view.contiguous(), b.contiguous(), None, 1.0, 0.0,
                               f"few rows, W^T, transposed A, m={m} k={k} n={n}")
-    # Through the Plan: the Finder's first choice for this layout is the few-rows kernel.
+    # Through the Plan: the Finder's first choice for this layout is a few-rows kernel, the exact one up to 16 rows.
     x = torch.randn(m, 2048, device="cuda")
     w = torch.randn(1024, 2048, device="cuda")
     d, names = gpu.gemm(x, w.t())
-    assert names[0] == ("Fp32GemmSkinny" if m <= 24 else "Fp32Gemm3xTf32SplitK"), names
+    assert names[0] == ("Fp32GemmSkinny" if m <= 16 else "Fp32Gemm3xTf32FewRows"), names
     check_against_float64(oracle, d, x, w.t().contiguous(), None, 1.0, 0.0, f"x @ W^T via {names[0]}")
 
 
@@ -508,7 +508,8 @@ def test_scatter_launch_adds_rows_into_owner_buffers(capi, gpu, oracle, kernel):
 
 
 def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle):
-    """Sixty seeded random problems: extents off every tile size, A and B plain or as transposed views
+    """Eighty seeded random problems (the last twenty with few rows of a row-major A and a K of 256 or
+    more, the few-rows tensor kernel's domain): extents off every tile size, A and B plain or as transposed views
     (pitches padded to keep them 16-byte aligned or deliberately not), C present or not, assorted
     scalars. Every family that accepts a problem must meet the float64 bar on it; the exact-FP32
     families are also held to the reference's tolerance against the sequential oracle when K is short."""
@@ -517,11 +518,12 @@ def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle
     rng = random.Random(20240611)
     torch.manual_seed(53)
     ran = {name: 0 for name in capi.KERNEL_NAMES.values()}
-    for case in range(60):
-        m = rng.choice([1, 2, 7, 17, 31, 33, 64, 100, 129, 200, 257, 384, 513])
+    for case in range(80):
+        few_rows = case >= 60
+        m = rng.choice([1, 2, 7, 17, 31, 33, 64] if few_rows else [1, 2, 7, 17, 31, 33, 64, 100, 129, 200, 257, 384, 513])
         n = rng.choice([1, 5, 32, 96, 100, 128, 131, 192, 260, 384, 500, 777])
-        k = rng.choice([1, 8, 31, 32, 33, 64, 100, 256, 300, 512, 1000, 2048, 4100])
-        a_t, b_t = rng.random() < 0.35, rng.random() < 0.35
+        k = rng.choice([256, 300, 512, 1000, 2048, 4100] if few_rows else [1, 8, 31, 32, 33, 64, 100, 256, 300, 512, 1000, 2048, 4100])
+        a_t, b_t = rng.random() < 0.35 and not few_rows, rng.random() < 0.35
         pad_a, pad_b = rng.choice([0, 0, 4, 3]), rng.choice([0, 0, 4, 1])
         a = (torch.randn(k, m + pad_a, device="cuda")[:, :m].t() if a_t else torch.randn(m, k + pad_a, device="cuda")[:, :k])
         b = (torch.randn(n, k + pad_b, device="cuda")[:, :k].t() if b_t else torch.randn(k, n + pad_b, device="cuda")[:, :n])
