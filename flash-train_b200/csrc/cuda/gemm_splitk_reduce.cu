@@ -8,6 +8,7 @@
 #include <cstdint>
 
 #include "gemm_kernels.hpp"
+#include "ptx.cuh"
 
 namespace ftcuda {
 namespace {
@@ -25,6 +26,9 @@ struct ReduceParams {
 };
 
 __global__ void __launch_bounds__(256) splitKReduce(const ReduceParams p) {
+    // Launched with programmatic stream serialization: the CTAs may be resident before the kernel
+    // that writes the partial sums has completed, and wait here for it.
+    gridDependencyWait();
     const std::uint64_t slab   = p.m * p.n;
     const std::uint64_t stride = static_cast<std::uint64_t>(gridDim.x) * blockDim.x;
     std::uint64_t index        = static_cast<std::uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -117,8 +121,16 @@ cudaError_t launchSplitKReduce(const FtcudaGemmDesc& desc, const float* partials
     std::uint64_t blocks       = ceilDiv(items, 256);
     if (blocks > 148 * 16) { blocks = 148 * 16; }
     if (blocks == 0) { blocks = 1; }
-    splitKReduce<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config{};
+    config.gridDim   = dim3(static_cast<unsigned>(blocks), 1, 1);
+    config.blockDim  = dim3(256, 1, 1);
+    config.stream    = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                         = &attribute;
+    config.numAttrs                                      = 1;
+    return cudaLaunchKernelEx(&config, splitKReduce, p);
 }
 
 }  // namespace ftcuda

@@ -137,6 +137,10 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         prefetchTensorMap(&map_b);
     }
     if (warp == kMmaWarp) { tmemAllocate(&bars->tmem_base, kTmemColumns); }
+    // The kernel after this one in the stream (the split-K reduction, launched with programmatic
+    // stream serialization) may place its CTAs as SMs come free; it waits for this grid's
+    // completion by itself before it reads the partial sums.
+    gridDependencyLaunchDependents();
     tcgen05FenceBeforeSync();
     __syncthreads();
     tcgen05FenceAfterSync();

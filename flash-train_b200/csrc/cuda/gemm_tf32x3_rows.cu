@@ -233,6 +233,10 @@ tensorGemm3xTf32Rows(const __grid_constant__ CUtensorMap map_a, const __grid_con
         prefetchTensorMap(&map_b);
     }
     if (warp == kMmaWarp) { tmemAllocate(&bars->tmem_base, kTmemColumns); }
+    // Everything above overlaps the tail of the kernel before this one in the stream; nothing below
+    // touches global memory before that kernel has completed.
+    gridDependencyWait();
+    gridDependencyLaunchDependents();
     tcgen05FenceBeforeSync();
     __syncthreads();
     tcgen05FenceAfterSync();
@@ -453,13 +457,17 @@ cudaError_t launchRowsPad(const LaunchState& state, const RowsParams& p, cudaStr
     config.blockDim         = dim3(state.block, 1, 1);
     config.dynamicSmemBytes = state.smem_bytes;
     config.stream           = stream;
-    cudaLaunchAttribute attribute{};
-    attribute.id               = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = 1;
-    attribute.val.clusterDim.y = state.grid_y;  // the K slices of a strip form one cluster
-    attribute.val.clusterDim.z = 1;
-    config.attrs               = &attribute;
-    config.numAttrs            = 1;
+    cudaLaunchAttribute attributes[2] = {};
+    attributes[0].id               = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 1;
+    attributes[0].val.clusterDim.y = state.grid_y;  // the K slices of a strip form one cluster
+    attributes[0].val.clusterDim.z = 1;
+    // The kernel waits for its predecessor in the stream by itself (gridDependencyWait), so its
+    // CTAs may start while that predecessor drains.
+    attributes[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                             = attributes;
+    config.numAttrs                                          = 2;
     return cudaLaunchKernelEx(&config, tensorGemm3xTf32Rows<kRowsPad>, state.map_a, state.map_b, p);
 }
 

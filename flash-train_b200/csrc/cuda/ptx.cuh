@@ -61,6 +61,21 @@ __device__ __forceinline__ bool mbarrierTryWait(std::uint64_t* barrier, std::uin
     return done != 0;
 }
 
+// Non-blocking test of the same condition (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbarrierTestWait(std::uint64_t* barrier, std::uint32_t parity) {
+    std::uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smemAddress(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Waits for the phase with the given parity to complete. Gives up -- returning
 // false -- when *abort_flag becomes nonzero or the time budget is exhausted.
 __device__ __forceinline__ bool mbarrierWait(std::uint64_t* barrier, std::uint32_t parity,
@@ -76,6 +91,20 @@ __device__ __forceinline__ bool mbarrierWait(std::uint64_t* barrier, std::uint32
         }
     }
 }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+
+// Blocks the calling thread until the grids this grid depends on (the kernels before it in the
+// stream) have completed and their memory operations are visible. Returns at once when the grid was
+// launched without programmatic stream serialization. Every thread that touches global memory
+// calls it first; what precedes it (barrier setup, tensor-memory allocation) overlaps the
+// predecessor's tail.
+__device__ __forceinline__ void gridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Lets the next grid in the stream (if it was launched with programmatic stream serialization)
+// start its CTAs as soon as every CTA of this grid has got here or exited. The dependent's own
+// gridDependencyWait still holds it back until this grid has completed.
+__device__ __forceinline__ void gridDependencyLaunchDependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- fences
 

@@ -36,7 +36,7 @@ def platform_gemm(capi, gpu, kernel, a, b, c, alpha, beta, d=None):
     """Runs one kernel family through ftcuda_gemm_configure / ftcuda_gemm_launch."""
     import os
 
-    if kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK) and os.environ.get("FT_SKIP_TENSOR"):
+    if kernel in (capi.KERNEL_TF32X3, capi.KERNEL_TF32X3_SPLITK, capi.KERNEL_TF32X3_ROWS) and os.environ.get("FT_SKIP_TENSOR"):
         return None, "tensor-core kernels switched off by FT_SKIP_TENSOR"
     m, n = a.shape[0], b.shape[1]
     if d is None:
