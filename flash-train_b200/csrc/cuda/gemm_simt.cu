@@ -209,6 +209,8 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 }
             }
         }
+        // This thread's reads of the stage (generic proxy) before its refill by TMA (async proxy).
+        fenceProxyAsync();
         __syncthreads();
     }
     if (!healthy) {
