@@ -22,6 +22,7 @@ enum Variant : int {
     kVariantMaskA    = 15,
     kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
     kVariantFlagPair = 32,  // tensor kernel: CTA pairs on 256-row tiles
+    kVariantFlagCluster = 64,  // tensor kernel: the K slices of a tile form a thread-block cluster (one launch)
 };
 
 // What ftcuda_gemm_configure stores inside an FtcudaGemmLaunch.

@@ -57,6 +57,8 @@
 #include <cstdlib>
 
 #include "gemm_kernels.hpp"
+#include <cooperative_groups.h>
+
 #include "ptx.cuh"
 #include "tf32x3_common.cuh"
 
@@ -107,6 +109,9 @@ struct Barriers {
     int abort_flag;
 };
 
+// kClustered: the cluster form (K slices of a tile as a thread-block cluster) is its own
+// instantiation, so that the plain form compiles exactly as it did without it.
+template<bool kClustered>
 __global__ void __launch_bounds__(kThreads, 1)
 tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const TensorParams p, const std::uint32_t num_items) {
@@ -156,7 +161,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item, kTileM);
+            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t use    = it / kRawSlots;
@@ -195,7 +200,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks = 0;  // chunks started so far, over all items
         bool ok              = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item, kTileM);
+            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const bool chunk_start = kb % p.chunk_k_blocks == 0;
                 if (chunk_start) {
@@ -255,7 +260,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem(p, item, kTileM);
+            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t s      = it % kStages;
@@ -351,7 +356,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks          = 0;
         bool ok                       = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w               = decodeItem(p, item, kTileM);
+            const WorkItem w               = decodeItem<kClustered>(p, item, kTileM);
             const std::uint32_t num_chunks = (w.k_blocks + p.chunk_k_blocks - 1) / p.chunk_k_blocks;
             const std::uint32_t row        = w.tile_m + lane_base + lane;
             const bool partial             = p.partials != nullptr;
@@ -386,7 +391,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
                     }
-                    if (last) {
+                    if (last && !kClustered) {
                         writeRowSegment(p, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
                     } else {
                         tmemStore16(tmem_row + kRunningColumn + col_half + piece * 16, sum);
@@ -410,10 +415,111 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         __syncthreads();
     }
+    if constexpr (kClustered) {
+        // ---- the K slices of this tile meet. Each CTA's sums sit in its running-sum columns. The
+        // twelve 16-column pieces of the tile are dealt out to the CTAs (piece q to rank q % ranks);
+        // a CTA sends the pieces it does not own to their owners' shared memory -- the raw slots,
+        // idle once every CTA of the cluster has left its main loop --, the owner adds the slices in
+        // rank order, applies alpha / beta and writes D.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster   = cg::this_cluster();
+        const std::uint32_t ranks   = p.cluster_ranks;
+        const std::uint32_t rank    = clusterCtaRank();
+        const std::uint32_t slots   = (2 * kPieces) / ranks;  // pieces per owner
+        float* receive              = reinterpret_cast<float*>(smem);  // [sender][slot][row][16]
+        const bool healthy          = *abort_flag == 0;
+        const int e                 = warp - kFirstEpilogue;
+        const std::uint32_t in_tile = static_cast<std::uint32_t>(32 * (e & 3) + lane);
+        const std::uint32_t half    = static_cast<std::uint32_t>(e >> 2);
+        const std::uint32_t tmem_at = tmem_base + ((32U * static_cast<std::uint32_t>(e & 3)) << 16) + kRunningColumn + half * kHalfColumns;
+        clusterBarrierArrive();
+        clusterBarrierWait();
+        if (warp >= kFirstEpilogue && warp < kFirstEpilogue + 8 && healthy) {
+            tcgen05FenceAfterSync();
+#pragma unroll
+            for (int piece = 0; piece < kPieces; ++piece) {
+                const std::uint32_t q     = half * kPieces + piece;
+                const std::uint32_t owner = q % ranks;
+                if (owner == rank) { continue; }
+                float sum[16];
+                tmemLoad16(tmem_at + piece * 16, sum);
+                float* remote = cluster.map_shared_rank(receive, owner) + ((rank * slots + q / ranks) * kTileM + in_tile) * 16;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    reinterpret_cast<float4*>(remote)[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+                }
+            }
+        }
+        clusterBarrierArrive();
+        clusterBarrierWait();
+        if (warp >= kFirstEpilogue && warp < kFirstEpilogue + 8 && healthy) {
+            tcgen05FenceAfterSync();
+            const WorkItem w        = decodeItem<kClustered>(p, blockIdx.x, kTileM);
+            const std::uint32_t row = w.tile_m + in_tile;
+            const bool vector_ok    = (p.n & 3) == 0 && (reinterpret_cast<std::uintptr_t>(p.d) & 15) == 0 && p.d_col_stride == 1 &&
+                                   (p.d_row_stride & 3) == 0 &&
+                                   (p.c == nullptr || (p.c_col_stride == 1 && (p.c_row_stride & 3) == 0 &&
+                                                       (reinterpret_cast<std::uintptr_t>(p.c) & 15) == 0));
+#pragma unroll
+            for (int piece = 0; piece < kPieces; ++piece) {
+                const std::uint32_t q = half * kPieces + piece;
+                if (q % ranks != rank) { continue; }
+                float own[16];
+                float sum[16];
+                tmemLoad16(tmem_at + piece * 16, own);
+                for (std::uint32_t r = 0; r < ranks; ++r) {
+                    const float4* part = reinterpret_cast<const float4*>(receive + ((r * slots + q / ranks) * kTileM + in_tile) * 16);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float4 v = r == rank ? make_float4(own[4 * j], own[4 * j + 1], own[4 * j + 2], own[4 * j + 3]) : part[j];
+                        if (r == 0) {
+                            sum[4 * j] = v.x, sum[4 * j + 1] = v.y, sum[4 * j + 2] = v.z, sum[4 * j + 3] = v.w;
+                        } else {
+                            sum[4 * j] += v.x, sum[4 * j + 1] += v.y, sum[4 * j + 2] += v.z, sum[4 * j + 3] += v.w;
+                        }
+                    }
+                }
+                writeRowSegment(p, w, row, w.tile_n + half * kHalfColumns + piece * 16, sum, vector_ok);
+            }
+        }
+        __syncthreads();
+    }
     if (warp == kMmaWarp) {
         tcgen05FenceAfterSync();
         tmemFree(tmem_base, kTmemColumns);
     }
+}
+
+// Clusters of `ranks` CTAs of the cluster form that the current device holds at once (0 on failure).
+int residentClusters(std::uint32_t ranks, std::uint32_t clusters_wanted) {
+    if (cudaFuncSetAttribute(tensorGemm3xTf32<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t config{};
+    config.gridDim          = dim3(clusters_wanted * ranks, 1, 1);
+    config.blockDim         = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attribute{};
+    attribute.id               = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = ranks;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs               = &attribute;
+    config.numAttrs            = 1;
+    int clusters               = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, tensorGemm3xTf32<true>, &config) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
+// FTCUDA_TF32_CLUSTER_SPLIT=0 keeps the single-launch family on one CTA per tile (read when a
+// launch is configured).
+bool clusterSplitEnabled() {
+    const char* text = std::getenv("FTCUDA_TF32_CLUSTER_SPLIT");
+    return text == nullptr || std::atoi(text) != 0;
 }
 
 // Number of K slices that fills the SMs in whole waves: the smallest count
@@ -522,6 +628,24 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
         state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
         return configureTensorPair(state, message, capacity);
     }
+    // Few tiles and a K worth cutting, in the single-launch family: the K slices of a tile become a
+    // thread-block cluster that meets through distributed shared memory -- no workspace, no second
+    // kernel. The twelve 16-column pieces of a tile are dealt out to the CTAs, hence 2, 3, 4 or 6.
+    if (!split_k && clusterSplitEnabled() && tiles * 2 <= static_cast<std::uint64_t>(sms) && desc.k >= 512) {
+        for (const std::uint32_t ranks : {6U, 4U, 3U, 2U}) {
+            if (tiles * ranks > static_cast<std::uint64_t>(sms) || desc.k / ranks < 256) { continue; }
+            const std::uint32_t per_slice = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, ranks), kTileK) * kTileK);
+            if (ceilDiv(desc.k, per_slice) != ranks) { continue; }  // every CTA of the cluster needs a slice
+            // All clusters have to be resident together (a second wave would double the time): a
+            // cluster lives inside one GPC, whose SM count need not be a multiple of the cluster size.
+            if (static_cast<std::uint64_t>(residentClusters(ranks, static_cast<std::uint32_t>(tiles))) < tiles) { continue; }
+            state.variant |= kVariantFlagCluster;
+            state.splits      = ranks;
+            state.k_per_split = per_slice;
+            break;
+        }
+    }
+    const bool clustered      = (state.variant & kVariantFlagCluster) != 0;
     const std::uint64_t items = tiles * state.splits;
     state.grid_x              = static_cast<std::uint32_t>(items < static_cast<std::uint64_t>(sms) ? items : sms);
     state.grid_y              = 1;
@@ -529,7 +653,8 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     state.block               = kThreads;
     state.smem_bytes          = kSmemBytes;
     state.chunk_k_blocks      = chunkKBlocks(desc.k);
-    state.workspace_bytes     = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
+    state.workspace_bytes =
+        state.splits > 1 && !clustered ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
     const bool a_encoded =
         (state.variant & kVariantMaskA) == kVariantTmaAk
             ? encodeTensorMap2d(&state.map_a, desc.a, desc.k, desc.m,
@@ -549,7 +674,8 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
                                            kSwizzle128, message, capacity);
     if (!b_encoded) { return 1; }
     const cudaError_t error =
-        cudaFuncSetAttribute(tensorGemm3xTf32, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaFuncSetAttribute(clustered ? tensorGemm3xTf32<true> : tensorGemm3xTf32<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemBytes);
     if (error != cudaSuccess) {
         return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error));
     }
@@ -589,15 +715,34 @@ TensorParams makeTensorParams(const LaunchState& state) {
 cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t stream) {
     const FtcudaGemmDesc& desc = state.desc;
     TensorParams p             = makeTensorParams(state);
-    p.partials                 = state.splits > 1 ? static_cast<float*>(workspace) : nullptr;
+    const bool clustered       = (state.variant & kVariantFlagCluster) != 0;
+    p.partials                 = state.splits > 1 && !clustered ? static_cast<float*>(workspace) : nullptr;
     cudaError_t error          = cudaSuccess;
+    if (clustered) {
+        p.cluster_ranks = state.splits;
+        cudaLaunchConfig_t config{};
+        config.gridDim          = dim3(state.grid_x, 1, 1);  // tiles x slices, all resident at once
+        config.blockDim         = dim3(state.block, 1, 1);
+        config.dynamicSmemBytes = state.smem_bytes;
+        config.stream           = stream;
+        cudaLaunchAttribute attribute{};
+        attribute.id               = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = state.splits;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs               = &attribute;
+        config.numAttrs            = 1;
+        error = cudaLaunchKernelEx(&config, tensorGemm3xTf32<true>, state.map_a, state.map_b, p, state.grid_x);
+        countLaunches(1);
+        return error;
+    }
     if ((state.variant & kVariantFlagPair) != 0) {
         p.tiles_m      = static_cast<std::uint32_t>(ceilDiv(desc.m, 2 * kTileM));
         p.band_m_tiles = p.band_m_tiles > 1 ? p.band_m_tiles / 2 : 1;
         error          = launchTensorPair(state, p, p.tiles_m * p.tiles_n * p.splits, stream);
     } else {
         const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
-        tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+        tensorGemm3xTf32<false><<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
         error = cudaGetLastError();
     }
     std::uint64_t launches = 1;
@@ -624,7 +769,7 @@ cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float
         for (std::uint32_t i = 0; i < owners && i < 8; ++i) { p.scatter[i] = owner_rows[i]; }
     }
     const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
-    tensorGemm3xTf32<<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+    tensorGemm3xTf32<false><<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
     cudaError_t error      = cudaGetLastError();
     std::uint64_t launches = 1;
     if (error == cudaSuccess && two_pass) {

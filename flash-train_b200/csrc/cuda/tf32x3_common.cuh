@@ -40,6 +40,9 @@ struct TensorParams {
     // may live on other GPUs (peer-mapped) -- instead of being written to d.
     float* scatter[8];
     std::uint32_t scatter_rows;
+    // Above 1: the K slices of a tile are the CTAs of a thread-block cluster (blockIdx.x = tile *
+    // cluster_ranks + slice, one work item per CTA) and meet through distributed shared memory.
+    std::uint32_t cluster_ranks;
     int* status;
 };
 
@@ -50,11 +53,13 @@ struct WorkItem {
 };
 
 // `tile_rows`: rows of A per work item (128 for one CTA, 256 for a CTA pair).
+template<bool kClustered = false>
 __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint32_t item, std::uint32_t tile_rows) {
     const std::uint32_t tiles = p.tiles_m * p.tiles_n;
     WorkItem w;
-    w.split                   = item / tiles;
-    const std::uint32_t tile  = item - w.split * tiles;
+    constexpr bool clustered  = kClustered;
+    w.split                   = clustered ? item % p.cluster_ranks : item / tiles;
+    const std::uint32_t tile  = clustered ? item / p.cluster_ranks : item - w.split * tiles;
     const std::uint32_t band  = tile / (p.band_m_tiles * p.tiles_n);
     const std::uint32_t first = band * p.band_m_tiles;
     const std::uint32_t rows  = min(p.band_m_tiles, p.tiles_m - first);

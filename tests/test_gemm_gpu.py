@@ -419,6 +419,8 @@ def test_cta_pair_form_of_the_tensor_kernel(capi, gpu, oracle, kernel, monkeypat
     if os.environ.get("FT_SKIP_TENSOR"):
         pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
     torch.manual_seed(43)
+    # The comparison is bit for bit, so the single-CTA form must not cut K over a cluster here.
+    monkeypatch.setenv("FTCUDA_TF32_CLUSTER_SPLIT", "0")
     for m, k, n, a_t, b_t in ((384, 320, 400, False, False), (256, 2304, 384, False, False), (700, 200, 4128, True, False),
                               (1024, 512, 768, False, True), (130, 96, 200, True, True)):
         a = torch.randn(k, m, device="cuda").t() if a_t else torch.randn(m, k, device="cuda")
@@ -548,6 +550,40 @@ def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle
                 assert ((d.double() - exact).abs() <= slack * (1.0 + scale)).all(), what
     # The draw must actually have exercised every family.
     assert all(count >= 5 for count in ran.values()), ran
+
+
+@pytest.mark.parametrize("m,k,n,ranks", [
+    (256, 3072, 384, 6),     # 4 tiles, six K slices
+    (384, 1024, 1152, 4),    # 18 tiles
+    (1024, 1024, 1024, 3),   # 48 tiles
+    (1024, 512, 1536, 2),    # 64 tiles, slices of 256
+    (300, 1000, 500, 3),     # ragged in m, n and K; the last slice is shorter
+    (130, 4100, 200, 6),     # one column of tiles off both tile extents, K off the K block
+])
+def test_tensor_kernel_splits_k_over_a_cluster(capi, gpu, oracle, m, k, n, ranks):
+    """Few tiles and a long enough K: the single-launch 3xTF32 family cuts K over a thread-block cluster
+    (one launch, no workspace) and the slices meet through distributed shared memory. With and without C,
+    B plain and as a transposed view, D written through a row pitch; results repeat bit for bit."""
+    import os
+
+    if os.environ.get("FT_SKIP_TENSOR"):
+        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
+    del ranks  # documents the expected cluster size; the library's choice is not visible through the ABI
+    torch.manual_seed(m + k + n)
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(k, n, device="cuda")
+    c = torch.randn(m, n, device="cuda")
+    for b_view in (b, b.t().contiguous().t()):
+        d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3, a, b_view, c, 1.5, -0.25)
+        assert d is not None, reason
+        check_against_float64(oracle, d, a, b, c, 1.5, -0.25, f"cluster split {m}x{k}x{n}")
+        again, _ = platform_gemm(capi, gpu, capi.KERNEL_TF32X3, a, b_view, c, 1.5, -0.25)
+        assert torch.equal(d, again), "the slices are added in rank order: results must repeat bit for bit"
+    d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3, a, b, None, 1.0, 0.0)
+    assert d is not None, reason
+    check_against_float64(oracle, d, a, b, None, 1.0, 0.0, f"cluster split, no C, {m}x{k}x{n}")
+    desc = capi.make_desc(gpu.operand(a), gpu.operand(b), capi.null_operand(m, n), gpu.operand(d), 1.0, 0.0, 0)
+    assert capi.PlatformGemm(capi.KERNEL_TF32X3, desc).workspace_bytes == 0
 
 
 @pytest.mark.parametrize("m", [1, 9, 16, 17, 32, 33, 64])
