@@ -58,14 +58,12 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         bool deep                  = false;  // too deep for eight K slices per strip
         if (shape.m <= 16) {
             rows_first = shape.k >= 1024 && shape.k * shape.n >= (8ULL << 20) && (!b_along_k || strips >= 32);
-            deep       = strips * 16 <= sm_count && shape.k >= 16384;
         } else if (shape.m <= 32) {
             rows_first = shape.k >= 2048 || (shape.k >= 1024 && strips >= 32);
-            deep       = strips * 16 <= sm_count && shape.k >= 16384;
         } else {
             rows_first = true;
-            deep       = strips * 8 <= sm_count && shape.k >= 4096;
         }
+        deep = strips * 16 <= sm_count && shape.k >= 32768;
         if (deep && (rows_first || shape.k >= 32768)) { return {tensor_split, tensor_rows, skinny, tensor, simt_split, simt}; }
         if (rows_first) { return {tensor_rows, tensor_split, skinny, tensor, simt_split, simt}; }
     }
@@ -86,6 +84,8 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 192);
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
         const bool ragged         = tiles * 10 < waves * sm_count * 9;  // the waves are under 90 % full overall
+        // (With few tiles the single-launch kernel cuts K over a thread-block cluster by itself; split-K
+        // with its finer slices still wins wherever the rules below prefer it, except 256 x 4096 x 4096.)
         if (ragged && shape.k >= 2048) { return {tensor_split, tensor, simt_split, simt}; }
         // A medium K is worth cutting (two launches, partial sums re-read by the
         // second) only while the tiles fill under a quarter of a wave.

@@ -252,8 +252,8 @@ TEST(finder_regime_map) {
     CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(65, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
     // Narrow and deep: eight K slices per strip are too few CTAs.
-    CHECK(first(64, 8192, 1024).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(64, 8192, 1024)[1] == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(64, 8192, 1024).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(48, 65536, 512)[1] == "Fp32Gemm3xTf32FewRows");
     CHECK(first(48, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(64, 256, 4096).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(65, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
@@ -266,7 +266,7 @@ TEST(finder_regime_map) {
     // Few rows but a narrow B: too few strips for the few-rows kernel.
     CHECK(first(17, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(17, 16384, 1024).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(17, 16384, 1024).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(8, 16384, 1024).front() == "Fp32GemmSkinny");
     CHECK(first(32, 4096, 2048).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(16, 4096, 2048).front() == "Fp32Gemm3xTf32FewRows");
