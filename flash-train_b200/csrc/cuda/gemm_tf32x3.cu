@@ -47,6 +47,16 @@
 // 216 KiB. Tensor memory: chunk 192 + running 192 + 2 stages x (A_hi 32 +
 // A_lo 32) columns = 512.
 //
+// Cluster form (template argument): when the tiles fill under half the SMs and K
+// is worth cutting, the grid is tiles x ranks CTAs, the `ranks` (2, 3, 4 or 6) K
+// slices of a tile forming a thread-block cluster, one work item per CTA. A CTA
+// keeps its slice's sums in the running-sum columns; after a cluster barrier
+// the twelve 16-column pieces of the tile are dealt out to the CTAs, every CTA
+// stores the pieces of the others into their shared memory (the raw slots, idle
+// by then) through distributed shared memory, and after a second cluster
+// barrier the owner of a piece adds the slices in rank order, scales and writes
+// D. One launch, no workspace, the same bits on every run.
+//
 // Every wait is bounded (ptx.cuh). A wait that gives up raises the CTA's abort
 // flag; all roles then stop, outstanding copies and MMAs are given time to
 // land, tensor memory is freed and the device status word is set to nonzero,
