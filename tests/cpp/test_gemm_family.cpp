@@ -245,8 +245,11 @@ TEST(finder_regime_map) {
     CHECK(first(12, 2048, 2048).front() == "Fp32GemmSkinny");
     CHECK(first(11, 4096, 4096).front() == "Fp32GemmSkinny");
     CHECK(first(17, 512, 4096).front() == "Fp32GemmSkinny");
-    // 2 x 22 tiles on 148 SMs and K long enough to cut: K slices first.
-    CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
+    // 2 x 22 tiles on 148 SMs, K = 4096: the single launch cuts K over clusters of three.
+    CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
+    // The same tiles with a deeper K, or half as many tiles: the two-launch split-K cuts finer.
+    CHECK(first(255, 16384, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(128, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(4097, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // From 33 rows on the tensor kernel's 128-row tile wins over the SIMT kernel.
     CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
@@ -262,7 +265,7 @@ TEST(finder_regime_map) {
     CHECK(first(64, 1024, 1024).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(96, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
-    CHECK(first(1024, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    CHECK(first(1024, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
     // Few rows but a narrow B: too few strips for the few-rows kernel.
     CHECK(first(17, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(1, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
