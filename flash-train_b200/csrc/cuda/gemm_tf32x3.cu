@@ -772,7 +772,8 @@ cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float
     TensorParams p = makeTensorParams(state);
     p.c            = nullptr;
     p.beta         = 0.0F;
-    const bool two_pass = workspace != nullptr && state.splits > 1;
+    // (The cluster form also has several K slices but no workspace: its slices add directly here.)
+    const bool two_pass = workspace != nullptr && state.splits > 1 && state.workspace_bytes > 0;
     p.partials          = two_pass ? static_cast<float*>(workspace) : nullptr;
     if (!two_pass) {
         p.scatter_rows = rows_per_owner;

@@ -146,8 +146,9 @@ FTCUDA_API uint64_t ftcuda_gemm_splitk_static_capacity(void);
  * is optional: without one (NULL, or fewer bytes than
  * ftcuda_gemm_workspace_bytes) every K slice of the split-K family adds its
  * tile directly, one launch, nothing stored; with one the slices are combined
- * on this GPU first and every element crosses NVLink once (two launches). The
- * order of the additions is not fixed, so the last bits of the result can
+ * on this GPU first and every element crosses NVLink once (two launches); a
+ * launch that asks for no workspace (ftcuda_gemm_workspace_bytes == 0) never
+ * writes to one. The order of the additions is not fixed, so the last bits of the result can
  * differ from run to run.
  */
 FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,

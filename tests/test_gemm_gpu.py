@@ -494,8 +494,9 @@ def test_scatter_launch_adds_rows_into_owner_buffers(capi, gpu, oracle, kernel):
             launch = capi.PlatformGemm(kernel, desc)
             size = launch.workspace_bytes if with_workspace else 0
             workspace = torch.empty(max(size, 1), dtype=torch.uint8, device="cuda")
-            launch.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream(),
-                               workspace.data_ptr() if size else 0, size)
+            # The pointer is never null: a workspace of fewer bytes than the launch asks for (here 0, also for
+            # the cluster form of the single-launch kernel, which asks for none) must be ignored, not written.
+            launch.run_scatter([block.data_ptr() for block in blocks], rows, gpu.current_stream(), workspace.data_ptr(), size)
         torch.cuda.synchronize()
         check_against_float64(oracle, torch.cat(blocks), a, b, c, alpha, beta,
                               f"scatter launch, {capi.KERNEL_NAMES[kernel]}, workspace={with_workspace}")
