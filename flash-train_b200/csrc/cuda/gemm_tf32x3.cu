@@ -683,9 +683,11 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
                                            static_cast<std::uint64_t>(desc.b_col_stride) * sizeof(float), kTileK, kTileN,
                                            kSwizzle128, message, capacity);
     if (!b_encoded) { return 1; }
-    const cudaError_t error =
-        cudaFuncSetAttribute(clustered ? tensorGemm3xTf32<true> : tensorGemm3xTf32<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemBytes);
+    // The plain form always: scatter launches use it even for a launch configured for the cluster form.
+    cudaError_t error = cudaFuncSetAttribute(tensorGemm3xTf32<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (error == cudaSuccess && clustered) {
+        error = cudaFuncSetAttribute(tensorGemm3xTf32<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    }
     if (error != cudaSuccess) {
         return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error));
     }
