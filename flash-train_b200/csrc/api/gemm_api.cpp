@@ -1,6 +1,10 @@
 // ftrainGemm: the one-shot call, built strictly on the staged C API.
 // Reference: src/api/gemm_api.cpp:28-83.
+#include <cstring>
+
 #include "api/api_support.hpp"
+#include "core/cache.hpp"
+#include "core/constraints.hpp"
 #include "core/trace.hpp"
 #include "flash_train/flash_train.h"
 
@@ -53,12 +57,145 @@ std::uint64_t pickPrimitive(FTrainPlan plan, const void* workspace, std::uint64_
     return 0;
 }
 
+// ---- per-thread memo of finished Plans -------------------------------------------------------
+// A training loop calls ftrainGemm with the same handful of (addresses, shapes, scalars) over and
+// over. Everything a Plan depends on is in the call's arguments -- the six views, the VALUES of alpha
+// and beta (a Plan reads them when it is created) and the calling thread's device --, so a call whose
+// arguments equal an earlier successful call's can execute that call's Plan again and skip Args,
+// Problem, key, cache lookup and launch configuration. The reference builds all of that per call
+// (src/api/gemm_api.cpp:54-83 there); the result is the same, only the host time differs.
+// Per thread, 64 entries, least recently used out first; calls whose arguments the memo cannot
+// describe (ranks other than the expected ones, non-FP32 or non-host scalars) and every failing call
+// take the ordinary path, and FTRAIN_DISABLE_CACHE switches the memo off with the selection cache.
+struct MemoView {
+    const void* memory;
+    std::int64_t dims[2];
+    std::int64_t strides[2];
+    std::uint8_t numeric_type, index_type, has_strides, is_host;
+};
+
+struct MemoKey {
+    MemoView matrices[4];
+    float alpha, beta;
+    std::int32_t device;
+    std::uint8_t compute_type;
+};
+
+bool describeMatrix(const FTrainStorageView& view, MemoView& out) noexcept {
+    if (view.num_dims != 2 || view.dims == nullptr) { return false; }
+    out.memory       = view.memory;
+    out.dims[0]      = view.dims[0];
+    out.dims[1]      = view.dims[1];
+    out.has_strides  = view.strides != nullptr ? 1 : 0;
+    out.strides[0]   = view.strides != nullptr ? view.strides[0] : 0;
+    out.strides[1]   = view.strides != nullptr ? view.strides[1] : 0;
+    out.numeric_type = view.numeric_type;
+    out.index_type   = view.index_type;
+    out.is_host      = view.is_host_memory ? 1 : 0;
+    return true;
+}
+
+bool readScalar(const FTrainStorageView& view, float& value) noexcept {
+    if (view.num_dims != 0 || view.memory == nullptr || !view.is_host_memory || view.strides != nullptr ||
+        view.numeric_type != FTRAIN_NUMERIC_TYPE_FP32 || view.index_type != FTRAIN_INDEX_TYPE_CONTINUOUS) {
+        return false;
+    }
+    std::memcpy(&value, view.memory, sizeof value);
+    return true;
+}
+
+class PlanMemo final {
+  public:
+    static constexpr int kEntries = 64;
+
+    ~PlanMemo() {
+        for (Entry& entry : entries_) { delete entry.plan; }  // not through the C API: its thread-local slot may be gone
+    }
+
+    FTrainPlan find(const MemoKey& key, std::uint64_t hash) noexcept {
+        for (Entry& entry : entries_) {
+            if (entry.plan != nullptr && entry.hash == hash && std::memcmp(&entry.key, &key, sizeof key) == 0) {
+                entry.last_use = ++clock_;
+                return entry.plan;
+            }
+        }
+        return nullptr;
+    }
+
+    // Takes ownership of `plan`; the least recently used entry makes room.
+    void insert(const MemoKey& key, std::uint64_t hash, FTrainPlan plan) noexcept {
+        Entry* victim = &entries_[0];
+        for (Entry& entry : entries_) {
+            if (entry.plan == nullptr) {
+                victim = &entry;
+                break;
+            }
+            if (entry.last_use < victim->last_use) { victim = &entry; }
+        }
+        delete victim->plan;
+        victim->key      = key;
+        victim->hash     = hash;
+        victim->plan     = plan;
+        victim->last_use = ++clock_;
+    }
+
+  private:
+    struct Entry {
+        MemoKey key;
+        std::uint64_t hash     = 0;
+        FTrainPlan plan        = nullptr;
+        std::uint64_t last_use = 0;
+    };
+    Entry entries_[kEntries];
+    std::uint64_t clock_ = 0;
+};
+
+std::uint64_t hashKey(const MemoKey& key) noexcept {
+    const unsigned char* bytes = reinterpret_cast<const unsigned char*>(&key);
+    std::uint64_t hash         = 0xcbf29ce484222325ULL;
+    for (std::size_t i = 0; i < sizeof key; i += 8) {
+        std::uint64_t word = 0;
+        std::memcpy(&word, bytes + i, sizeof key - i < 8 ? sizeof key - i : 8);
+        hash = (hash ^ word) * 0x100000001b3ULL;
+        hash ^= hash >> 29;
+    }
+    return hash;
+}
+
+// Fills `key` (zeroed first, padding included, so that keys compare bytewise) when the memo can
+// describe the call.
+bool makeMemoKey(const FTrainStorageView& a, const FTrainStorageView& b, const FTrainStorageView& c, const FTrainStorageView& d,
+                 const FTrainStorageView& alpha, const FTrainStorageView& beta, FTrainNumericType compute_type,
+                 MemoKey& key) noexcept {
+    if (ftrain::isSelectionCacheDisabled()) { return false; }
+    std::memset(&key, 0, sizeof key);
+    if (!describeMatrix(a, key.matrices[0]) || !describeMatrix(b, key.matrices[1]) || !describeMatrix(c, key.matrices[2]) ||
+        !describeMatrix(d, key.matrices[3]) || !readScalar(alpha, key.alpha) || !readScalar(beta, key.beta)) {
+        return false;
+    }
+    key.compute_type = static_cast<std::uint8_t>(compute_type);
+    try {
+        key.device = ftrain::getCurrentDeviceId();
+    } catch (...) { return false; }  // the ordinary path reports the failure
+    return true;
+}
+
 }  // namespace
 
 extern "C" FTrainStatus ftrainGemm(FTrainStorageView a, FTrainStorageView b, FTrainStorageView c, FTrainStorageView d,
                                    FTrainStorageView alpha, FTrainStorageView beta, FTrainNumericType compute_type,
                                    void* workspace, uint64_t workspace_bytes, FTrainStream stream) {
     ftrain::ScopedTraceRange trace("ftrainGemm");
+    static thread_local PlanMemo memo;
+    MemoKey key;
+    const bool memoised      = makeMemoKey(a, b, c, d, alpha, beta, compute_type, key);
+    const std::uint64_t hash = memoised ? hashKey(key) : 0;
+    if (memoised) {
+        if (FTrainPlan known = memo.find(key, hash)) {
+            return ftrainPlanExecutePrimitive(known, pickPrimitive(known, workspace, workspace_bytes), workspace,
+                                              workspace_bytes, stream);
+        }
+    }
     const GemmEntry& entry = gemmEntry();
     if (entry.status != FTRAIN_STATUS_SUCCESS) { return entry.status; }
 
@@ -82,8 +219,13 @@ extern "C" FTrainStatus ftrainGemm(FTrainStorageView a, FTrainStorageView b, FTr
     // The clean-up calls below overwrite the thread's last result; the failing
     // call's diagnostic is what the caller must see.
     if (status == FTRAIN_STATUS_SUCCESS) {
-        if (plan != nullptr) { ftrainPlanDestroy(plan); }
+        if (memoised) {
+            memo.insert(key, hash, plan);  // kept for the next call with these arguments
+        } else if (plan != nullptr) {
+            ftrainPlanDestroy(plan);
+        }
         if (args != nullptr) { ftrainArgsDestroy(args); }
+        ftrain::clearLastResult();
         return status;
     }
     const ftrain::Result failure = ftrain::getLastResult();

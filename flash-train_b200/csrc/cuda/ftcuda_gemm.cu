@@ -64,11 +64,10 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
         return ftcuda::fail(message, message_capacity, 1, "workspace of %llu bytes needed",
                             static_cast<unsigned long long>(state.workspace_bytes));
     }
-    // A kernel of an earlier launch on this device gave up on a wait: the
-    // device-side pipeline is not trustworthy any more.
-    if (state.host_status != nullptr && *state.host_status != 0) {
-        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)",
-                            *state.host_status);
+    // A kernel of an earlier launch on this device gave up on a wait (its results are not valid):
+    // reported once, here, and cleared -- the kernel left in order, so later launches may proceed.
+    if (const int code = ftcuda::takeDeviceStatus(state.host_status)) {
+        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)", code);
     }
     const cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
     cudaError_t error              = cudaSuccess;
@@ -104,9 +103,8 @@ extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* 
     for (int32_t i = 0; i < owners; ++i) {
         if (owner_rows[i] == nullptr) { return ftcuda::fail(message, message_capacity, 1, "owner %d has no buffer", i); }
     }
-    if (state.host_status != nullptr && *state.host_status != 0) {
-        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)",
-                            *state.host_status);
+    if (const int code = ftcuda::takeDeviceStatus(state.host_status)) {
+        return ftcuda::fail(message, message_capacity, 1, "an earlier kernel reported a timed-out wait (code %d)", code);
     }
     // A workspace is optional here; one that is too small is ignored (direct adds).
     if (workspace_bytes < state.workspace_bytes) { workspace = nullptr; }

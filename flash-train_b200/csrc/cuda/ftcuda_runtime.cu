@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "gemm_kernels.hpp"
+#include "ptx.cuh"
 
 namespace ftcuda {
 namespace {
@@ -33,6 +34,38 @@ DeviceInfo& deviceInfo(int device) {
 }
 
 std::atomic<std::uint64_t> g_launches{0};
+
+// FP32 FFMA throughput probe: eight independent accumulator chains per thread, 32 FFMAs per loop trip.
+__global__ void __launch_bounds__(1024) ffmaRateProbe(float* sink, float x, float y, int trips) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { acc[i] = 1e-3F * static_cast<float>(threadIdx.x) + static_cast<float>(i); }
+    for (int trip = 0; trip < trips; ++trip) {
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { acc[i] = fmaf(acc[i], x, y); }
+        }
+    }
+    float total = 0.0F;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { total += acc[i]; }
+    if (total == 12345.678F && sink != nullptr) { *sink = total; }  // keeps the chains alive; never true in practice
+}
+
+// One warp waiting on a barrier nobody arrives on: the give-up path of every bounded wait.
+__global__ void boundedWaitProbe(int* status, unsigned long long budget_ns) {
+    __shared__ std::uint64_t barrier;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbarrierInit(&barrier, 1);
+        abort_flag = 0;
+        fenceBarrierInit();
+    }
+    __syncthreads();
+    const bool completed = mbarrierWaitFor(&barrier, 0, &abort_flag, budget_ns);
+    if (!completed && threadIdx.x == 0 && status != nullptr) { *status = 2; }
+}
 
 PFN_cuTensorMapEncodeTiled_v12000 tensorMapEncoder() {
     // Resolved through the runtime so the library needs no link-time libcuda.
@@ -77,7 +110,7 @@ bool deviceSmCount(int device, int* sm_count, char* message, std::size_t capacit
     return true;
 }
 
-bool deviceStatusWord(int device, int** device_pointer, const volatile int** host_pointer, char* message,
+bool deviceStatusWord(int device, int** device_pointer, volatile int** host_pointer, char* message,
                       std::size_t capacity) {
     if (device < 0 || device >= kMaxDevices) {
         fail(message, capacity, 1, "device %d is out of range", device);
@@ -160,6 +193,74 @@ extern "C" int ftcuda_device_sm_count(int32_t device, int32_t* sm_count, char* m
     int count = 0;
     if (!ftcuda::deviceSmCount(device, &count, message, message_capacity)) { return 1; }
     *sm_count = count;
+    return 0;
+}
+
+extern "C" int ftcuda_device_status(int32_t device, int32_t* code, char* message, size_t message_capacity) {
+    if (code == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null argument"); }
+    int* device_side          = nullptr;
+    volatile int* host_side   = nullptr;
+    if (!ftcuda::deviceStatusWord(device, &device_side, &host_side, message, message_capacity)) { return 1; }
+    *code = *host_side;
+    return 0;
+}
+
+extern "C" int ftcuda_device_status_reset(int32_t device, char* message, size_t message_capacity) {
+    int* device_side        = nullptr;
+    volatile int* host_side = nullptr;
+    if (!ftcuda::deviceStatusWord(device, &device_side, &host_side, message, message_capacity)) { return 1; }
+    *host_side = 0;
+    return 0;
+}
+
+extern "C" int ftcuda_selftest_bounded_wait(int32_t device, uint64_t budget_ns, void* stream, char* message,
+                                            size_t message_capacity) {
+    if (budget_ns > 1000000000ULL) { return ftcuda::fail(message, message_capacity, 1, "the budget is at most one second"); }
+    int current       = -1;
+    cudaError_t error = cudaGetDevice(&current);
+    if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+    if (current != device) { return ftcuda::fail(message, message_capacity, 1, "device %d must be current", device); }
+    int* device_side        = nullptr;
+    volatile int* host_side = nullptr;
+    if (!ftcuda::deviceStatusWord(device, &device_side, &host_side, message, message_capacity)) { return 1; }
+    ftcuda::boundedWaitProbe<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_side, budget_ns);
+    error = cudaGetLastError();
+    if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+    return 0;
+}
+
+extern "C" int ftcuda_measure_ffma_tflops(int32_t device, double* tflops, char* message, size_t message_capacity) {
+    if (tflops == nullptr) { return ftcuda::fail(message, message_capacity, 1, "null argument"); }
+    int current       = -1;
+    cudaError_t error = cudaGetDevice(&current);
+    if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+    if (current != device) { return ftcuda::fail(message, message_capacity, 1, "device %d must be current", device); }
+    int sms = 0;
+    if (!ftcuda::deviceSmCount(device, &sms, message, message_capacity)) { return 1; }
+    cudaEvent_t begin = nullptr, end = nullptr;
+    if ((error = cudaEventCreate(&begin)) != cudaSuccess || (error = cudaEventCreate(&end)) != cudaSuccess) {
+        if (begin != nullptr) { cudaEventDestroy(begin); }
+        return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error));
+    }
+    constexpr int kTrips = 4096;                 // x 32 FFMAs per thread
+    const int blocks     = 2 * sms;              // 2048 threads per SM
+    double best_ms       = 0.0;
+    for (int attempt = 0; attempt < 4 && error == cudaSuccess; ++attempt) {  // the first launch warms up
+        cudaEventRecord(begin, nullptr);
+        ftcuda::ffmaRateProbe<<<blocks, 1024>>>(nullptr, 0.999F, 1e-3F, kTrips);
+        cudaEventRecord(end, nullptr);
+        error = cudaEventSynchronize(end);
+        float ms = 0.0F;
+        if (error == cudaSuccess) { error = cudaEventElapsedTime(&ms, begin, end); }
+        if (attempt > 0 && (best_ms == 0.0 || ms < best_ms)) { best_ms = ms; }
+    }
+    cudaEventDestroy(begin);
+    cudaEventDestroy(end);
+    if (error != cudaSuccess || best_ms <= 0.0) {
+        return ftcuda::fail(message, message_capacity, 1, "FFMA probe failed: %s", cudaGetErrorString(error));
+    }
+    const double flops = 2.0 * 32.0 * kTrips * 1024.0 * blocks;
+    *tflops            = flops / (best_ms * 1e-3) / 1e12;
     return 0;
 }
 

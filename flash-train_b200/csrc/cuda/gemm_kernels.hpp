@@ -39,9 +39,10 @@ struct LaunchState {
     std::uint32_t k_per_split;     // K elements per slice, a multiple of the K tile
     std::uint32_t chunk_k_blocks;  // tensor kernel: K blocks accumulated in TMEM between drains
     std::uint32_t row_tile;        // skinny kernel: rows of A kept per thread
+    std::uint32_t band_m_tiles;    // tensor kernel: M tiles walked together (fixed when the launch is configured)
     std::uint64_t workspace_bytes;
     int* device_status;            // mapped host word the kernels report a timed-out wait in
-    const volatile int* host_status;
+    volatile int* host_status;
 };
 static_assert(sizeof(LaunchState) <= sizeof(FtcudaGemmLaunch), "launch blob too small");
 static_assert(alignof(FtcudaGemmLaunch) >= 64, "launch blob must be 64-byte aligned");
@@ -57,8 +58,15 @@ int fail(char* message, std::size_t capacity, int code, const char* format, ...)
 bool deviceSmCount(int device, int* sm_count, char* message, std::size_t capacity);
 // Per-device status word in mapped pinned host memory; nonzero after a kernel
 // gave up on a wait. Returns false (with message) on a CUDA error.
-bool deviceStatusWord(int device, int** device_pointer, const volatile int** host_pointer, char* message,
+bool deviceStatusWord(int device, int** device_pointer, volatile int** host_pointer, char* message,
                       std::size_t capacity);
+// Reads the status word of a launch's device and clears it: a timed-out wait is reported once.
+inline int takeDeviceStatus(volatile int* host_status) {
+    if (host_status == nullptr) { return 0; }
+    const int code = *host_status;
+    if (code != 0) { *host_status = 0; }
+    return code;
+}
 // Shared-memory swizzle of a tiled copy. kSwizzle128: 16-byte chunks of a 128-byte
 // row XOR-ed with row % 8. kSwizzle128Atom32: 32-byte chunks XOR-ed with row % 4
 // (the layout the tensor cores want for an MN-major operand of 32-bit elements).

@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(256) splitKReduceScatter(const ScatterReducePa
         const std::uint64_t row   = index / p.n;
         const std::uint64_t col   = index % p.n;
         const std::uint64_t owner = row / p.rows_per_owner;
-        atomicAdd(p.owner_rows[owner] + (row - owner * p.rows_per_owner) * p.n + col, p.alpha * sum);
+        // System scope: several GPUs add into the same peer-mapped element at once.
+        atomicAdd_system(p.owner_rows[owner] + (row - owner * p.rows_per_owner) * p.n + col, p.alpha * sum);
     }
 }
 

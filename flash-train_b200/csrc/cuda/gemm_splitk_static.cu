@@ -46,23 +46,39 @@ constexpr int kMaxDevices              = 64;
 static __device__ __align__(256) float g_scratch[kScratchFloats];
 
 struct DeviceScratch {
-    std::once_flag once;
-    cudaError_t error = cudaSuccess;
-    float* address    = nullptr;
+    std::mutex mutex;
+    bool resolved  = false;
+    float* address = nullptr;
 };
 
 DeviceScratch g_device_scratch[kMaxDevices];
 
-// The device address of g_scratch on `device`, which must be current.
+// The device address of g_scratch on `device`, which must be current. Only a successful lookup is
+// remembered: one that failed (for instance because the first call came during a stream capture)
+// is tried again by the next call, and the error it left in the runtime is cleared.
 cudaError_t scratchAddress(int device, float** address) {
     DeviceScratch& slot = g_device_scratch[device];
-    std::call_once(slot.once, [&slot] {
-        void* pointer = nullptr;
-        slot.error    = cudaGetSymbolAddress(&pointer, g_scratch);
+    std::lock_guard<std::mutex> guard(slot.mutex);
+    if (!slot.resolved) {
+        void* pointer           = nullptr;
+        const cudaError_t error = cudaGetSymbolAddress(&pointer, g_scratch);
+        if (error != cudaSuccess || pointer == nullptr) {
+            (void)cudaGetLastError();
+            *address = nullptr;
+            return error != cudaSuccess ? error : cudaErrorInvalidSymbol;
+        }
         slot.address  = static_cast<float*>(pointer);
-    });
+        slot.resolved = true;
+    }
     *address = slot.address;
-    return slot.error;
+    return cudaSuccess;
+}
+
+// True once the array's address on `device` is known (no lookup is needed any more).
+bool scratchResolved(int device) {
+    DeviceScratch& slot = g_device_scratch[device];
+    std::lock_guard<std::mutex> guard(slot.mutex);
+    return slot.resolved;
 }
 
 }  // namespace
@@ -118,6 +134,16 @@ extern "C" int ftcuda_gemm_splitk_static(const FtcudaGemmDesc* desc, void* strea
                     static_cast<unsigned long long>(state.workspace_bytes));
     }
 
+    // The first call on a device looks the array up, which is not allowed while the stream is being
+    // captured: say so instead of invalidating the capture.
+    if (!scratchResolved(desc->device)) {
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capture) != cudaSuccess) { (void)cudaGetLastError(); }
+        if (capture != cudaStreamCaptureStatusNone) {
+            return fail(message, message_capacity, 1,
+                        "the first call on a device resolves the static scratch and must come before stream capture");
+        }
+    }
     float* scratch = nullptr;
     error          = scratchAddress(desc->device, &scratch);
     if (error != cudaSuccess || scratch == nullptr) {

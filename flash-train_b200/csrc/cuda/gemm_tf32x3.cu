@@ -573,7 +573,7 @@ std::uint32_t chunkKBlocks(std::uint64_t k) {
 
 // Output tiles are walked in bands of this many M tiles (all N tiles of a band
 // before the next band): every band re-reads B once from HBM while its A
-// panels (band x 128 rows x K) stay in L2. FTCUDA_TF32_BAND_M_TILES overrides.
+// panels (band x 128 rows x K) stay in L2. FTCUDA_TF32_BAND_M_TILES overrides (read when a launch is configured).
 std::uint32_t bandMTiles() {
     const char* text = std::getenv("FTCUDA_TF32_BAND_M_TILES");
     if (text != nullptr) {
@@ -613,6 +613,7 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
     if (!deviceSmCount(desc.device, &sms, message, capacity)) { return 1; }
     if (!deviceStatusWord(desc.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
     state.variant = tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m) ? kVariantTmaAk : kVariantTmaAm;
+    state.band_m_tiles = bandMTiles();  // environment switches are read here, never on the launch path
     const bool b_n_contiguous = tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
     if (!b_n_contiguous) { state.variant |= kVariantFlagBk; }
     const std::uint64_t tiles  = ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
@@ -713,7 +714,7 @@ TensorParams makeTensorParams(const LaunchState& state) {
     p.splits         = state.splits;
     p.k_per_split    = state.k_per_split;
     p.chunk_k_blocks = state.chunk_k_blocks;
-    p.band_m_tiles   = bandMTiles();
+    p.band_m_tiles   = state.band_m_tiles;
     p.a_m_contiguous = (state.variant & kVariantMaskA) == kVariantTmaAm ? 1U : 0U;
     p.b_k_contiguous = (state.variant & kVariantFlagBk) != 0 ? 1U : 0U;
     p.alpha          = desc.alpha;

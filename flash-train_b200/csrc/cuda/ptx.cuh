@@ -77,9 +77,9 @@ __device__ __forceinline__ bool mbarrierTestWait(std::uint64_t* barrier, std::ui
 }
 
 // Waits for the phase with the given parity to complete. Gives up -- returning
-// false -- when *abort_flag becomes nonzero or the time budget is exhausted.
-__device__ __forceinline__ bool mbarrierWait(std::uint64_t* barrier, std::uint32_t parity,
-                                             const volatile int* abort_flag) {
+// false -- when *abort_flag becomes nonzero or `budget_ns` has elapsed.
+__device__ __forceinline__ bool mbarrierWaitFor(std::uint64_t* barrier, std::uint32_t parity,
+                                                const volatile int* abort_flag, unsigned long long budget_ns) {
     if (mbarrierTryWait(barrier, parity)) { return true; }
     const unsigned long long start = globalTimerNs();
     std::uint32_t spins            = 0;
@@ -87,9 +87,15 @@ __device__ __forceinline__ bool mbarrierWait(std::uint64_t* barrier, std::uint32
         if (mbarrierTryWait(barrier, parity)) { return true; }
         if ((++spins & 0xFF) == 0) {
             if (*abort_flag != 0) { return false; }
-            if (globalTimerNs() - start > kWaitBudgetNs) { return false; }
+            if (globalTimerNs() - start > budget_ns) { return false; }
         }
     }
+}
+
+// The same with the kernels' budget.
+__device__ __forceinline__ bool mbarrierWait(std::uint64_t* barrier, std::uint32_t parity,
+                                             const volatile int* abort_flag) {
+    return mbarrierWaitFor(barrier, parity, abort_flag, kWaitBudgetNs);
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

@@ -77,14 +77,28 @@ __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint3
 // instructions: the conversion unit has a fraction of the ALU's throughput and
 // the converter warps are on the kernel's critical path. Adding half a TF32 ulp
 // to the sign-magnitude bit pattern and clearing the low 13 bits rounds the
-// magnitude; infinities stay infinities.
+// magnitude. Only for values whose rounding cannot carry into the exponent
+// field 0xFF (the low part of a split, see splitTf32).
 __device__ __forceinline__ std::uint32_t tf32Round(float value) {
     return (__float_as_uint(value) + 0x1000U) & 0xFFFFE000U;
 }
 
-// value = hi + lo (+ a remainder below 2^-22 |value|), both TF32.
+// The same rounding, saturated at the largest finite TF32 magnitude (0x7F7FE000): a finite value
+// within half a TF32 ulp of FLT_MAX would otherwise round up to infinity. Infinities and NaNs also
+// come out as that finite magnitude, which is what splitTf32 wants of its high part.
+__device__ __forceinline__ std::uint32_t tf32RoundSaturated(float value) {
+    const std::uint32_t bits  = __float_as_uint(value);
+    const std::uint32_t limit = (bits & 0x80000000U) | 0x7F7FFFFFU;  // largest finite pattern of this sign
+    return min(bits + 0x1000U, limit) & 0xFFFFE000U;
+}
+
+// value = hi + lo (+ a remainder below 2^-22 |value|), both TF32. The high part is always finite,
+// so the low part is exact for every finite input, FLT_MAX included. For value = +-inf the high part
+// is the largest TF32 number and the low part is +-inf, for a NaN the low part is a NaN: the three
+// products a_lo b_hi + a_hi b_lo + a_hi b_hi then give what IEEE FP32 arithmetic gives for the
+// product -- +-inf, or NaN for inf * 0 and inf - inf -- and not a NaN from inf - inf inside the split.
 __device__ __forceinline__ void splitTf32(float value, std::uint32_t& hi, std::uint32_t& lo) {
-    hi = tf32Round(value);
+    hi = tf32RoundSaturated(value);
     lo = tf32Round(value - __uint_as_float(hi));
 }
 
@@ -103,9 +117,10 @@ static __device__ __noinline__ void writeRowSegmentSlow(float* out, std::int64_t
 }
 
 // Scatter mode: adds scale * sum[j] to target[j] for the (up to 16) columns left in the row. K slices of
-// this GPU and of other GPUs all add into the owner's rows; the order of the additions is not fixed.
+// this GPU and of other GPUs all add into the owner's rows; the order of the additions is not fixed. The
+// atomics have system scope: device-scope atomics of different GPUs are not atomic with one another.
 static __device__ __noinline__ void addRowSegment(float* target, float scale, std::uint32_t columns_left, const float* sum) {
-    for (std::uint32_t j = 0; j < 16 && j < columns_left; ++j) { atomicAdd(target + j, scale * sum[j]); }
+    for (std::uint32_t j = 0; j < 16 && j < columns_left; ++j) { atomicAdd_system(target + j, scale * sum[j]); }
 }
 
 // Writes one row segment of 16 consecutive columns held by one thread.

@@ -58,10 +58,12 @@ class GemmProblem final {
     // c and d are the same address: D is accumulated in place.
     bool isInPlace() const noexcept { return getAddress(GemmPort::kC) == getAddress(GemmPort::kD); }
 
-    // Everything that can change which Primitive applies or wins, as tokens.
-    // Each field is introduced by a running field number and variable-length
-    // fields carry their length, so distinct descriptions cannot alias.
-    // Addresses enter only through null-ness, alignment class and aliasing.
+    // Everything that can change which Primitive applies or wins, as tokens: per
+    // view a fixed head (types, rank and stride count packed into one word;
+    // has-memory; address modulo 16; length of the tail) and then its extents and
+    // strides, after the six views the compute type and the in-place flag. The
+    // heads carry the lengths, so distinct descriptions cannot alias. Addresses
+    // enter only through null-ness, alignment class and aliasing.
     std::vector<std::uint64_t> getProblemKey() const;
 
   private:

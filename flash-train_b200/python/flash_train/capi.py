@@ -49,7 +49,8 @@ EXPORTED_SYMBOLS = (
 PLATFORM_SYMBOLS = (
     "ftcuda_current_device ftcuda_device_sm_count ftcuda_gemm_supports ftcuda_gemm_configure "
     "ftcuda_gemm_workspace_bytes ftcuda_gemm_launch ftcuda_launch_count ftcuda_trace_push ftcuda_trace_pop "
-    "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity ftcuda_gemm_launch_scatter"
+    "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity ftcuda_gemm_launch_scatter "
+    "ftcuda_device_status ftcuda_device_status_reset ftcuda_selftest_bounded_wait ftcuda_measure_ffma_tflops"
 ).split()
 
 
@@ -413,8 +414,14 @@ def _declare_platform(lib) -> None:
                                                c_void_p] + message
     lib.ftcuda_gemm_splitk_static_capacity.argtypes = []
     lib.ftcuda_gemm_splitk_static_capacity.restype = c_uint64
+    lib.ftcuda_device_status.argtypes = [ctypes.c_int32, POINTER(ctypes.c_int32)] + message
+    lib.ftcuda_device_status_reset.argtypes = [ctypes.c_int32] + message
+    lib.ftcuda_selftest_bounded_wait.argtypes = [ctypes.c_int32, c_uint64, c_void_p] + message
+    lib.ftcuda_measure_ffma_tflops.argtypes = [ctypes.c_int32, POINTER(ctypes.c_double)] + message
+    lib.ftcuda_measure_ffma_tflops.restype = ctypes.c_int
     for name in ("ftcuda_current_device", "ftcuda_device_sm_count", "ftcuda_gemm_supports", "ftcuda_gemm_configure",
-                 "ftcuda_gemm_launch", "ftcuda_gemm_splitk_static", "ftcuda_gemm_launch_scatter"):
+                 "ftcuda_gemm_launch", "ftcuda_gemm_splitk_static", "ftcuda_gemm_launch_scatter", "ftcuda_device_status",
+                 "ftcuda_device_status_reset", "ftcuda_selftest_bounded_wait"):
         getattr(lib, name).restype = ctypes.c_int
 
 
@@ -478,3 +485,34 @@ def splitk_static(desc: GemmDesc, stream: int = 0) -> None:
 
 def splitk_static_capacity() -> int:
     return int(lib.ftcuda_gemm_splitk_static_capacity())
+
+
+def device_status(device: int = 0) -> int:
+    """ftcuda_device_status: the device's status word (0 = no kernel has given up on a wait since it was last cleared)."""
+    code = ctypes.c_int32(0)
+    buffer = ctypes.create_string_buffer(256)
+    if lib.ftcuda_device_status(device, byref(code), buffer, 256) != 0:
+        raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
+    return int(code.value)
+
+
+def device_status_reset(device: int = 0) -> None:
+    buffer = ctypes.create_string_buffer(256)
+    if lib.ftcuda_device_status_reset(device, buffer, 256) != 0:
+        raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
+
+
+def selftest_bounded_wait(device: int, budget_ns: int, stream: int = 0) -> None:
+    """ftcuda_selftest_bounded_wait: one warp waits `budget_ns` on a barrier nothing arrives on, then sets the status word."""
+    buffer = ctypes.create_string_buffer(256)
+    if lib.ftcuda_selftest_bounded_wait(device, budget_ns, c_void_p(stream), buffer, 256) != 0:
+        raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
+
+
+def measure_ffma_tflops(device: int = 0) -> float:
+    """ftcuda_measure_ffma_tflops: the device's measured FP32 FFMA rate (register-only probe kernel)."""
+    value = ctypes.c_double(0.0)
+    buffer = ctypes.create_string_buffer(256)
+    if lib.ftcuda_measure_ffma_tflops(device, byref(value), buffer, 256) != 0:
+        raise FTrainError(STATUS_INTERNAL_ERROR, buffer.value.decode())
+    return float(value.value)

@@ -13,15 +13,23 @@
 //     ftrainGemm makes (Args, Plan, execute primitive 0) and, in between, asks
 //     the Plan how much workspace primitive 0 wants and takes it from torch's
 //     caching allocator;
-//   * a failure carries the library's diagnostic message, not only the status.
+//   * a failure carries the library's diagnostic message, not only the status;
+//   * the Plans of recent calls are kept per thread (64, least recently used out first), keyed by
+//     the four addresses, the shape, alpha, beta and the device: a training loop that calls with
+//     the same tensors again executes the kept Plan and skips Args and Plan creation. The output
+//     tensor comes from torch's caching allocator, which hands a loop the same blocks again and
+//     again. FTRAIN_DISABLE_CACHE switches this off together with the library's selection cache.
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 #include <optional>
 #include <string>
 
+#include <flash_train/env.h>
 #include <flash_train/flash_train.h>
 
 namespace {
@@ -72,6 +80,74 @@ const GemmRoles& gemmRoles() {
     return roles;
 }
 
+// Plans of this thread's recent calls. Everything a Plan depends on is in the key.
+struct CallKey {
+    const void* a;
+    const void* b;
+    const void* c;
+    const void* d;
+    std::int64_t m, k, n;
+    float alpha, beta;
+    std::int32_t device;
+    std::int32_t zero;  // explicit padding: keys are compared bytewise
+};
+
+class RecentPlans final {
+  public:
+    struct Entry {
+        CallKey key{};
+        FTrainPlan plan               = nullptr;
+        std::uint64_t workspace_bytes = 0;
+        std::uint64_t last_use        = 0;
+    };
+
+    ~RecentPlans() {
+        for (Entry& entry : entries_) {
+            if (entry.plan != nullptr) { ftrainPlanDestroy(entry.plan); }
+        }
+    }
+
+    Entry* find(const CallKey& key) noexcept {
+        for (Entry& entry : entries_) {
+            if (entry.plan != nullptr && std::memcmp(&entry.key, &key, sizeof key) == 0) {
+                entry.last_use = ++clock_;
+                return &entry;
+            }
+        }
+        return nullptr;
+    }
+
+    void insert(const CallKey& key, FTrainPlan plan, std::uint64_t workspace_bytes) noexcept {
+        Entry* victim = &entries_[0];
+        for (Entry& entry : entries_) {
+            if (entry.plan == nullptr) {
+                victim = &entry;
+                break;
+            }
+            if (entry.last_use < victim->last_use) { victim = &entry; }
+        }
+        if (victim->plan != nullptr) { ftrainPlanDestroy(victim->plan); }
+        *victim = Entry{key, plan, workspace_bytes, ++clock_};
+    }
+
+  private:
+    Entry entries_[64];
+    std::uint64_t clock_ = 0;
+};
+
+bool planReuseDisabled() {
+    static const bool disabled = [] {
+        const char* text = std::getenv(FTRAIN_DISABLE_CACHE);
+        if (text == nullptr) { return false; }
+        std::string value(text);
+        const auto first = value.find_first_not_of(" \t");
+        const auto last  = value.find_last_not_of(" \t");
+        value            = first == std::string::npos ? std::string() : value.substr(first, last - first + 1);
+        return !value.empty() && value != "0";
+    }();
+    return disabled;
+}
+
 at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const std::optional<at::Tensor>& c, double alpha,
                 double beta) {
     checkMatrix(a, "a");
@@ -94,6 +170,34 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const std::optional<at
     const float alpha_value       = static_cast<float>(alpha);
     const float beta_value        = static_cast<float>(beta);
     const auto stream = reinterpret_cast<FTrainStream>(c10::cuda::getCurrentCUDAStream(a.device().index()).stream());
+
+    static thread_local RecentPlans recent;
+    const bool reuse = !planReuseDisabled();
+    CallKey key;
+    std::memset(&key, 0, sizeof key);
+    key.a      = a.data_ptr();
+    key.b      = b.data_ptr();
+    key.c      = c.has_value() ? c->data_ptr() : nullptr;
+    key.d      = d.data_ptr();
+    key.m      = a.size(0);
+    key.k      = a.size(1);
+    key.n      = b.size(1);
+    key.alpha  = alpha_value;
+    key.beta   = beta_value;
+    key.device = a.device().index();
+    if (reuse) {
+        if (RecentPlans::Entry* known = recent.find(key)) {
+            at::Tensor scratch;
+            if (known->workspace_bytes != 0) {
+                scratch = torch::empty({static_cast<std::int64_t>(known->workspace_bytes)}, a.options().dtype(at::kByte));
+            }
+            const FTrainStatus again = ftrainPlanExecutePrimitive(
+                known->plan, 0, known->workspace_bytes != 0 ? scratch.data_ptr() : nullptr, known->workspace_bytes, stream);
+            TORCH_CHECK(again == FTRAIN_STATUS_SUCCESS, "flash_train gemm failed with status ", static_cast<unsigned>(again), ": ",
+                        ftrainGetLastMessage());
+            return d;
+        }
+    }
 
     const GemmRoles& roles = gemmRoles();
     TORCH_CHECK(roles.status == FTRAIN_STATUS_SUCCESS, "flash_train could not set up its Gemm Ops, status ",
@@ -128,6 +232,10 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const std::optional<at
                                             workspace_bytes, stream);
     }
     const std::string failure = status == FTRAIN_STATUS_SUCCESS ? std::string() : std::string(ftrainGetLastMessage());
+    if (status == FTRAIN_STATUS_SUCCESS && reuse) {
+        recent.insert(key, plan, workspace_bytes);  // kept for the next call with these tensors
+        plan = nullptr;
+    }
     if (plan != nullptr) { ftrainPlanDestroy(plan); }
     if (args != nullptr) { ftrainArgsDestroy(args); }
     TORCH_CHECK(status == FTRAIN_STATUS_SUCCESS, "flash_train gemm failed with status ", static_cast<unsigned>(status),

@@ -10,6 +10,11 @@ device buffers per banded operand, events in between. Every band is one
 ordinary `flash_train.torch.gemm` call, so kernel selection, the selection
 cache and the numerics are those of the library.
 
+Several GPUs multiplying their own rows of A by the SAME B (the row-sharded GEMM): given a process
+group, every rank uploads only its 1/world share of B's rows and the ranks exchange the shares over
+NVLink with one all-gather (NCCL), so that B crosses each GPU's PCIe link once in total instead of once
+per GPU.
+
 The reference has no counterpart: its binding takes device tensors only
 (python/flash_train/torch/csrc/flash_train_torch.cpp:34-75 there).
 """
@@ -49,10 +54,21 @@ class HostGemm:
     but its copies do not overlap.
     """
 
-    def __init__(self, m: int, n: int, k: int, device=None, band_rows: int = DEFAULT_BAND_ROWS, with_c: bool = False):
+    def __init__(self, m: int, n: int, k: int, device=None, band_rows: int = DEFAULT_BAND_ROWS, with_c: bool = False,
+                 group=None):
+        """group: a torch.distributed process group whose ranks all call with the same host matrix B (each
+        with its own rows of A): every rank then uploads rows [rank * k / world, (rank + 1) * k / world)
+        of B only and receives the others' rows by an all-gather over NVLink. k must divide evenly."""
         from . import gemm as device_gemm
 
         self._gemm = device_gemm
+        self._group, self._world, self._rank = None, 1, 0
+        if group is not None:
+            import torch.distributed as dist
+
+            world = dist.get_world_size(group)
+            if world > 1 and k % world == 0:
+                self._group, self._world, self._rank = group, world, dist.get_rank(group)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.bands = band_ranges(m, band_rows)
@@ -92,7 +108,16 @@ class HostGemm:
             copy_in.wait_stream(compute)
             copy_in.wait_stream(copy_out)
             with torch.cuda.stream(copy_in):
-                self._b.copy_(b, non_blocking=True)
+                if self._group is None:
+                    self._b.copy_(b, non_blocking=True)
+                else:
+                    import torch.distributed as dist
+
+                    share = self.k // self._world
+                    mine = slice(self._rank * share, (self._rank + 1) * share)
+                    self._b[mine].copy_(b[mine], non_blocking=True)
+                    # In place: the share already lies where the gathered matrix wants it.
+                    dist.all_gather_into_tensor(self._b, self._b[mine], group=self._group)
             band_used = [None, None]  # event: kernels of the band that last used buffer pair i are done
             for index, (start, stop) in enumerate(self.bands):
                 pair, rows = index % 2, stop - start

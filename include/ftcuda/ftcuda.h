@@ -155,6 +155,34 @@ FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* 
                                           float* const* owner_rows, int32_t owners, uint64_t rows_per_owner, void* stream,
                                           char* message, size_t message_capacity);
 
+/*
+ * Per-device status word (no counterpart in the reference, whose kernel has no device-side waits).
+ * Every wait inside the kernels is bounded; a kernel whose wait ran out stops its pipeline, frees
+ * its tensor memory, returns, and leaves a nonzero code in a word of mapped host memory. The next
+ * ftcuda_gemm_launch / ftcuda_gemm_launch_scatter on that device reports the code as a failure ONCE and
+ * clears it, so later launches proceed (the context is intact: nothing trapped). ftcuda_device_status
+ * reads the word without clearing it (0 = healthy; *code is 0 for a device no launch was configured
+ * on yet), ftcuda_device_status_reset clears it.
+ */
+FTCUDA_API int ftcuda_device_status(int32_t device, int32_t* code, char* message, size_t message_capacity);
+FTCUDA_API int ftcuda_device_status_reset(int32_t device, char* message, size_t message_capacity);
+
+/*
+ * Self test of the bounded wait: launches one warp on `stream` that waits, with a budget of
+ * `budget_ns` nanoseconds (at most one second), on a barrier nothing ever arrives on, and then
+ * records code 2 in the device's status word -- the path a kernel takes when a partner role has
+ * stopped, without a trap, a fault or an unbounded spin. `device` must be current.
+ */
+FTCUDA_API int ftcuda_selftest_bounded_wait(int32_t device, uint64_t budget_ns, void* stream, char* message,
+                                            size_t message_capacity);
+
+/*
+ * Measured FP32 FFMA rate of `device` (which must be current) in TFLOP/s: a register-only kernel of
+ * independent FFMA chains, 2048 threads per SM, best of three launches timed with CUDA events on the
+ * default stream; blocks until done. The yardstick the exact-FP32 kernels are held against.
+ */
+FTCUDA_API int ftcuda_measure_ffma_tflops(int32_t device, double* tflops, char* message, size_t message_capacity);
+
 /* Number of device kernels ftcuda_gemm_launch has enqueued from this process;
  * benchmarks read it to report how many launches a timed region made. */
 FTCUDA_API uint64_t ftcuda_launch_count(void);

@@ -19,7 +19,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = Path(os.environ.get("FTRAIN_REFERENCE", "/root/reference"))
+# The reference checkout: $FTRAIN_REFERENCE, else a directory named "reference" beside this repository.
+REFERENCE = Path(os.environ["FTRAIN_REFERENCE"]) if os.environ.get("FTRAIN_REFERENCE") else HERE.parent.parent / "reference"
 
 
 def _run(command: list[str]) -> None:

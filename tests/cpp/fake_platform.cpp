@@ -69,8 +69,13 @@ extern "C" int ftcuda_gemm_supports(int kernel, const FtcudaGemmDesc* desc, char
     }
 }
 
-extern "C" int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, FtcudaGemmLaunch* launch, char*, size_t) {
+extern "C" int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, FtcudaGemmLaunch* launch, char* message,
+                                     size_t capacity) {
     ++fake::state().configures;
+    if (const char* reason = fake::state().fail_next_configure) {
+        fake::state().fail_next_configure = nullptr;
+        return fake::fail(message, capacity, reason);
+    }
     std::memset(launch, 0, sizeof *launch);
     auto* blob      = reinterpret_cast<fake::Blob*>(launch);
     blob->kernel    = kernel;
@@ -86,7 +91,11 @@ extern "C" uint64_t ftcuda_gemm_workspace_bytes(const FtcudaGemmLaunch* launch) 
 }
 
 extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
-                                  void* stream, char*, size_t) {
+                                  void* stream, char* message, size_t capacity) {
+    if (const char* reason = fake::state().fail_next_launch) {
+        fake::state().fail_next_launch = nullptr;
+        return fake::fail(message, capacity, reason);
+    }
     const auto* blob = reinterpret_cast<const fake::Blob*>(launch);
     fake::state().launches.push_back(fake::LaunchRecord{blob->kernel, workspace, workspace_bytes, stream, blob->desc});
     return 0;

@@ -29,6 +29,10 @@ struct State {
     std::vector<LaunchRecord> launches;
     int configures = 0;
     int supports   = 0;
+    // Host-side failure injection: the next configure / launch call answers with this reason (and
+    // clears it), the way the real layer reports a failed cudaFuncSetAttribute or kernel launch.
+    const char* fail_next_configure = nullptr;
+    const char* fail_next_launch    = nullptr;
 };
 
 State& state();

@@ -239,12 +239,138 @@ TEST(one_shot_gemm_walks_the_workspace_budget) {
     char buffer[8];
     CHECK_EQ(static_cast<int>(call(buffer, 1 << 20)), 0);
     CHECK_EQ(fake::state().launches.back().kernel, static_cast<int>(FTCUDA_GEMM_TF32X3_SPLITK));
+    // A workspace smaller than primitive 0 asks for (the fake's split-K kernels want 4096 bytes) is
+    // walked past like no workspace at all; one of exactly the required size selects primitive 0.
+    CHECK_EQ(static_cast<int>(call(buffer, 4095)), 0);
+    CHECK_EQ(fake::state().launches.back().kernel, static_cast<int>(FTCUDA_GEMM_TF32X3));
+    CHECK_EQ(fake::state().launches.back().workspace_bytes, std::uint64_t{4095});
+    CHECK_EQ(static_cast<int>(call(buffer, 4096)), 0);
+    CHECK_EQ(fake::state().launches.back().kernel, static_cast<int>(FTCUDA_GEMM_TF32X3_SPLITK));
     // A failing call leaves its own diagnostic as the thread's last message.
     const std::int64_t wrong[2] = {5, 5};
     CHECK_EQ(static_cast<int>(ftrainGemm(matrix(address(0x10000), a_dims), matrix(address(0x20000), wrong), matrix(nullptr, d_dims),
                                          matrix(address(0x40000), d_dims), scalar(&alpha), scalar(&beta), FTRAIN_NUMERIC_TYPE_FP32,
                                          nullptr, 0, nullptr)),
              static_cast<int>(FTRAIN_STATUS_INVALID_ARGUMENT));
-    CHECK(std::strstr(ftrainGetLastMessage(), "does not match b row count") != nullptr);
+    CHECK(std::strstr(ftrainGetLastMessage(), "columns but b has") != nullptr);
+    fake::reset();
+}
+
+// A failed kernel launch or a failed launch configuration surfaces as INTERNAL_ERROR with the platform's
+// reason in the message (the reference maps hipGetLastError the same way,
+// src/primitive/hygon/gemm/fp32_gemm.hip:47-50, through the catch-all of src/include/flash_train/api.hpp:36-62);
+// the Plan stays valid and destroyable, and the next call is clean.
+TEST(one_shot_and_staged_calls_report_injected_platform_failures) {
+    fake::reset();
+    GemmGraph g = makeGraph();
+    FTrainOps ops = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, g.pattern)), 0);
+    FTrainArgs args = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainArgsCreate(&args, ops)), 0);
+    const std::int64_t a_dims[2] = {512, 1024}, b_dims[2] = {1024, 768}, d_dims[2] = {512, 768};
+    float alpha = 1.0F, beta = 0.0F;
+    ftrainArgsSetTensor(args, g.a, matrix(address(0x10000), a_dims));
+    ftrainArgsSetTensor(args, g.b, matrix(address(0x20000), b_dims));
+    ftrainArgsSetTensor(args, g.c, matrix(nullptr, d_dims));
+    ftrainArgsSetTensor(args, g.d, matrix(address(0x40000), d_dims));
+    ftrainArgsSetTensor(args, g.alpha, scalar(&alpha));
+    ftrainArgsSetTensor(args, g.beta, scalar(&beta));
+    CHECK_EQ(static_cast<int>(ftrainArgsSetGemm(args, g.op, FTRAIN_NUMERIC_TYPE_FP32)), 0);
+
+    // Configure fails: no Plan, the caller's variable untouched, the reason in the message.
+    FTrainPlan plan = reinterpret_cast<FTrainPlan>(0x5);
+    fake::state().fail_next_configure = "cudaFuncSetAttribute failed: injected";
+    CHECK_EQ(static_cast<int>(ftrainPlanCreate(&plan, args)), static_cast<int>(FTRAIN_STATUS_INTERNAL_ERROR));
+    CHECK(plan == reinterpret_cast<FTrainPlan>(0x5));
+    CHECK(std::strstr(ftrainGetLastMessage(), "configuring the launch failed: cudaFuncSetAttribute failed: injected") != nullptr);
+    CHECK_EQ(static_cast<int>(ftrainGetLastStatus()), static_cast<int>(FTRAIN_STATUS_INTERNAL_ERROR));
+
+    // The same Args make a Plan once the platform answers again.
+    plan = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainPlanCreate(&plan, args)), 0);
+    CHECK(plan != nullptr);
+    std::uint64_t bytes = 0;
+    CHECK_EQ(static_cast<int>(ftrainPlanGetPrimitiveRequiredWorkspaceBytes(plan, 0, &bytes)), 0);
+    char workspace[8];
+    void* const pointer = bytes != 0 ? workspace : nullptr;
+
+    // Launch fails: INTERNAL_ERROR, nothing recorded as launched, the Plan still answers queries.
+    const std::size_t launched = fake::state().launches.size();
+    fake::state().fail_next_launch = "an illegal memory access was encountered (injected)";
+    CHECK_EQ(static_cast<int>(ftrainPlanExecutePrimitive(plan, 0, pointer, bytes, nullptr)),
+             static_cast<int>(FTRAIN_STATUS_INTERNAL_ERROR));
+    CHECK(std::strstr(ftrainGetLastMessage(), "kernel launch failed: an illegal memory access was encountered (injected)") != nullptr);
+    CHECK_EQ(fake::state().launches.size(), launched);
+    CHECK_EQ(static_cast<int>(ftrainGetLastStatus()), static_cast<int>(FTRAIN_STATUS_INTERNAL_ERROR));
+    std::uint64_t count = 0;
+    CHECK_EQ(static_cast<int>(ftrainPlanGetNumPrimitives(plan, &count)), 0);
+    CHECK(count >= 1);
+
+    // The next execute of the same Plan is clean and reaches the platform.
+    CHECK_EQ(static_cast<int>(ftrainPlanExecutePrimitive(plan, 0, pointer, bytes, nullptr)), 0);
+    CHECK_EQ(fake::state().launches.size(), launched + 1);
+    CHECK_EQ(static_cast<int>(ftrainGetLastStatus()), 0);
+    CHECK_EQ(std::strlen(ftrainGetLastMessage()), std::size_t{0});
+
+    // The one-shot call carries the launch failure through its own clean-up.
+    fake::state().fail_next_launch = "unspecified launch failure (injected)";
+    CHECK_EQ(static_cast<int>(ftrainGemm(matrix(address(0x10000), a_dims), matrix(address(0x20000), b_dims), matrix(nullptr, d_dims),
+                                         matrix(address(0x40000), d_dims), scalar(&alpha), scalar(&beta), FTRAIN_NUMERIC_TYPE_FP32,
+                                         nullptr, 0, nullptr)),
+             static_cast<int>(FTRAIN_STATUS_INTERNAL_ERROR));
+    CHECK(std::strstr(ftrainGetLastMessage(), "unspecified launch failure (injected)") != nullptr);
+
+    CHECK_EQ(static_cast<int>(ftrainPlanDestroy(plan)), 0);
+    CHECK_EQ(static_cast<int>(ftrainArgsDestroy(args)), 0);
+    CHECK_EQ(static_cast<int>(ftrainOpsDestroy(ops)), 0);
+    CHECK_EQ(static_cast<int>(ftrainPatternDestroy(g.pattern)), 0);
+    fake::reset();
+}
+
+// The one-shot call keeps the Plans of its recent calls per thread: equal arguments (addresses, shapes,
+// the VALUES of alpha and beta, device) execute the kept Plan again without configuring anything; any
+// difference makes a new Plan, as the reference's per-call Plan would be (src/api/gemm_api.cpp:54-83 there).
+TEST(one_shot_gemm_reuses_the_plan_of_an_equal_call) {
+    fake::reset();
+    const std::int64_t a_dims[2] = {640, 512}, b_dims[2] = {512, 384}, d_dims[2] = {640, 384};
+    float alpha = 1.0F, beta = 0.0F;
+    const auto call = [&](std::uintptr_t a_address) {
+        return ftrainGemm(matrix(address(a_address), a_dims), matrix(address(0x200000), b_dims), matrix(nullptr, d_dims),
+                          matrix(address(0x400000), d_dims), scalar(&alpha), scalar(&beta), FTRAIN_NUMERIC_TYPE_FP32, nullptr, 0,
+                          nullptr);
+    };
+    CHECK_EQ(static_cast<int>(call(0x100000)), 0);
+    const int configured = fake::state().configures;
+    const std::size_t launched = fake::state().launches.size();
+    CHECK(configured >= 1);
+    CHECK_EQ(static_cast<int>(call(0x100000)), 0);
+    CHECK_EQ(fake::state().configures, configured);            // nothing configured again
+    CHECK_EQ(fake::state().launches.size(), launched + 1);     // but launched again, with the same description
+    CHECK(fake::state().launches.back().desc.a == address(0x100000));
+    CHECK_EQ(static_cast<int>(ftrainGetLastStatus()), 0);
+    // The scalars are compared by value, as a Plan reads them when it is made: a changed alpha is another Plan...
+    alpha = 2.5F;
+    CHECK_EQ(static_cast<int>(call(0x100000)), 0);
+    CHECK(fake::state().configures > configured);
+    CHECK_EQ(fake::state().launches.back().desc.alpha, 2.5F);
+    // ...and so is another address.
+    const int after_alpha = fake::state().configures;
+    CHECK_EQ(static_cast<int>(call(0x180000)), 0);
+    CHECK(fake::state().configures > after_alpha);
+    CHECK(fake::state().launches.back().desc.a == address(0x180000));
+    // The first pair of values is still remembered.
+    alpha = 1.0F;
+    const int before = fake::state().configures;
+    CHECK_EQ(static_cast<int>(call(0x100000)), 0);
+    CHECK_EQ(fake::state().configures, before);
+    CHECK_EQ(fake::state().launches.back().desc.alpha, 1.0F);
+    // Another current device: a Plan of its own (Plans are bound to their device).
+    fake::state().device = 3;
+    CHECK_EQ(static_cast<int>(call(0x100000)), 0);
+    CHECK(fake::state().configures > before);
+    // More distinct calls than the memo holds: still correct, the oldest simply are planned again.
+    fake::state().device = 0;
+    for (std::uintptr_t i = 0; i < 80; ++i) { CHECK_EQ(static_cast<int>(call(0x1000000 + i * 0x10000)), 0); }
+    CHECK(fake::state().launches.back().desc.a == address(0x1000000 + 79 * 0x10000));
     fake::reset();
 }

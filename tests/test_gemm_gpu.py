@@ -289,23 +289,39 @@ def test_config3_tail_sweep_contiguous_and_transposed(capi, gpu, oracle, m):
     check_against_float64(oracle, once, a, b, None, 1.0, 0.0, f"m={m} one-shot")
 
 
-def test_config4_training_shape_rows_sampled(capi, gpu, oracle):
+def check_whole_matrix_in_row_blocks(oracle, d, a, b, what, block_rows):
+    """Every element of d against a float64 product, `block_rows` rows at a time (to bound memory): the
+    scaled error is taken per block and the worst block has to meet the bar against the worst block of
+    torch's FP32 product."""
+    b64 = b.double()
+    col_norms = b64.norm(dim=0, keepdim=True)
+    ours = torch_error = 0.0
+    for start in range(0, a.shape[0], block_rows):
+        rows = slice(start, min(start + block_rows, a.shape[0]))
+        a64 = a[rows].double()
+        exact = a64 @ b64
+        scale = a64.norm(dim=1, keepdim=True) * col_norms + 1e-300
+        assert torch.isfinite(d[rows]).all(), f"{what}: non-finite output in rows {rows}"
+        ours = max(ours, float(((d[rows].double() - exact).abs() / scale).max()))
+        torch_error = max(torch_error, float((((a[rows] @ b).double() - exact).abs() / scale).max()))
+        del a64, exact, scale
+    assert ours <= 2.0 * max(torch_error, ERROR_FLOOR), f"{what}: scaled error {ours:.3e} vs torch FP32 {torch_error:.3e}"
+    return ours, torch_error
+
+
+def test_config4_training_shape_whole_matrix(capi, gpu, oracle):
     m, k, n = 16384, 4096, 14336
     torch.manual_seed(3)
     a = torch.randn(m, k, device="cuda")
     b = torch.randn(k, n, device="cuda") / (k ** 0.5)
     d, names = gpu.gemm(a, b)
     assert names[0] == "Fp32Gemm3xTf32"
-    rows = torch.tensor([0, 1, 127, 128, 4095, 8191, 8192, 16383], device="cuda")
-    check_against_float64(oracle, d[rows], a[rows], b, None, 1.0, 0.0, "config 4 sampled rows")
-    # Whole-matrix property: D @ ones == A @ (B @ ones) up to rounding.
-    ones = torch.ones(n, 1, device="cuda", dtype=torch.float64)
-    lhs = d.double() @ ones
-    rhs = a.double() @ (b.double() @ ones)
-    assert torch.allclose(lhs, rhs, rtol=1e-6, atol=1e-3)
+    # All 128 x 75 output tiles of every band, not a sample of rows.
+    report = check_whole_matrix_in_row_blocks(oracle, d, a, b, "config 4, all rows", 2048)
+    print("config4 scaled errors (ours, torch fp32):", report)
 
 
-def test_config5_tall_k_split(capi, gpu, oracle):
+def test_config5_tall_k_split_whole_matrix(capi, gpu, oracle):
     m = n = 2048
     k = 262144
     generator = torch.Generator(device="cuda").manual_seed(4)
@@ -313,8 +329,9 @@ def test_config5_tall_k_split(capi, gpu, oracle):
     b = torch.rand(k, n, device="cuda", generator=generator) * 2 - 1
     d, names = gpu.gemm(a, b)
     assert names[0] == "Fp32Gemm3xTf32SplitK"
-    rows = torch.tensor([0, 5, 1023, 2047], device="cuda")
-    check_against_float64(oracle, d[rows], a[rows], b, None, 1.0, 0.0, "config 5 sampled rows")
+    # The float64 copy of B alone is 4 GiB; 256 rows of A at a time keep the rest small.
+    report = check_whole_matrix_in_row_blocks(oracle, d, a, b, "config 5, all rows", 256)
+    print("config5 scaled errors (ours, torch fp32):", report)
 
 
 def test_plan_reuse_many_executions(capi, gpu):
@@ -619,3 +636,84 @@ def test_tensor_few_rows_kernel(capi, gpu, oracle, m):
                          torch.randn(512, 256, device="cuda"), None, 1.0, 0.0)[0] is None
     assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, torch.randn(8, 64, device="cuda"), torch.randn(64, 256, device="cuda"),
                          None, 1.0, 0.0)[0] is None
+
+
+@pytest.mark.parametrize("kernel", [1, 2, 5])
+def test_split_precision_kernels_keep_ieee_behaviour_at_the_edge_of_the_range(capi, gpu, oracle, kernel):
+    """Infinities, NaN and +-FLT_MAX in A and B: the 3xTF32 kernels must give what the exact FFMA kernel
+    (FTCUDA_GEMM_SIMT, the reference's arithmetic) gives -- +-inf where it gives +-inf, NaN where it gives
+    NaN (inf - inf, inf * 0, NaN), finite and close where it is finite. The high part of the split
+    saturates at the largest finite TF32 number, so FLT_MAX neither rounds up to infinity nor turns into
+    a NaN inside the split."""
+    import os
+
+    if os.environ.get("FT_SKIP_TENSOR"):
+        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
+    flt_max = torch.finfo(torch.float32).max
+    torch.manual_seed(61)
+    m, k, n = (48, 1024, 384) if kernel == 5 else (256, 1024, 384)
+    a = torch.rand(m, k, device="cuda") * 0.5 + 0.25
+    b = torch.rand(k, n, device="cuda") * 0.25 + 0.125   # positive, so that a row's infinities do not cancel
+    a[1, 5] = float("inf")
+    a[2, 700] = float("-inf")
+    a[3, 9], a[3, 600] = float("inf"), float("-inf")       # inf - inf -> NaN
+    a[4, 33] = float("nan")
+    a[5, 100] = flt_max                                     # times at most 0.375: finite
+    a[6, 1000] = -flt_max
+    a[7, 64] = float("inf")
+    b[64, 17] = 0.0                                         # inf * 0 -> NaN in column 17 of row 7
+    b[200, 40] = float("inf")                               # a whole column of +inf
+    b[300, 41] = -flt_max * 0.5                             # times at most 0.75: finite
+    expected, reason = platform_gemm(capi, gpu, capi.KERNEL_SIMT, a, b, None, 1.0, 0.0)
+    assert expected is not None, reason
+    d, reason = platform_gemm(capi, gpu, kernel, a, b, None, 1.0, 0.0)
+    if d is None:
+        pytest.skip(f"{capi.KERNEL_NAMES[kernel]} declines: {reason}")
+    name = capi.KERNEL_NAMES[kernel]
+    assert torch.equal(torch.isnan(d), torch.isnan(expected)), f"{name}: NaN pattern differs from the FFMA kernel's"
+    infinite = torch.isinf(expected)
+    assert torch.equal(torch.isinf(d), infinite), f"{name}: infinity pattern differs from the FFMA kernel's"
+    assert torch.equal(d[infinite], expected[infinite]), f"{name}: an infinity has the wrong sign"
+    finite = torch.isfinite(expected)
+    assert finite[5].all() and finite[6].all() and finite[:, 41].sum() >= m - 6, "the FLT_MAX lines are meant to stay finite"
+    assert torch.allclose(d[finite], expected[finite], rtol=2e-5, atol=1e-3), f"{name}: finite entries are off"
+
+
+def test_a_wait_that_runs_out_is_reported_once_and_the_device_stays_usable(capi, gpu):
+    """The give-up path of the kernels' bounded waits, made to happen without a fault: one warp waits
+    200 microseconds on a barrier nothing arrives on, returns, and leaves code 2 in the device's status
+    word. The next launch reports it (once), the one after runs and is correct; a reset clears it too."""
+    device = torch.cuda.current_device()
+    a, b = torch.randn(256, 512, device="cuda"), torch.randn(512, 384, device="cuda")
+    d = torch.empty(256, 384, device="cuda")
+    desc = capi.make_desc(gpu.operand(a), gpu.operand(b), capi.null_operand(256, 384), gpu.operand(d), 1.0, 0.0, device)
+    launch = capi.PlatformGemm(capi.KERNEL_SIMT, desc)
+    launch.run(0, 0, gpu.current_stream())
+    torch.cuda.synchronize()
+    assert capi.device_status(device) == 0
+    capi.selftest_bounded_wait(device, 200_000, gpu.current_stream())
+    torch.cuda.synchronize()  # the kernel returned by itself
+    assert capi.device_status(device) == 2
+    with pytest.raises(capi.FTrainError, match="timed-out wait"):
+        launch.run(0, 0, gpu.current_stream())
+    assert capi.device_status(device) == 0
+    d.fill_(float("nan"))
+    launch.run(0, 0, gpu.current_stream())
+    torch.cuda.synchronize()
+    assert torch.allclose(d, a @ b, rtol=1e-4, atol=1e-3)
+    # Through the public API the same condition is INTERNAL_ERROR, then clean again.
+    capi.selftest_bounded_wait(device, 200_000, gpu.current_stream())
+    torch.cuda.synchronize()
+    plan = gpu.make_plan(a, b, None, d)
+    with pytest.raises(capi.FTrainError) as info:
+        gpu.run_plan(plan)
+    assert info.value.status == capi.STATUS_INTERNAL_ERROR and "timed-out wait" in info.value.message
+    gpu.run_plan(plan)
+    torch.cuda.synchronize()
+    capi.selftest_bounded_wait(device, 200_000, gpu.current_stream())
+    torch.cuda.synchronize()
+    capi.device_status_reset(device)
+    assert capi.device_status(device) == 0
+    gpu.run_plan(plan)
+    torch.cuda.synchronize()
+    assert torch.allclose(d, a @ b, rtol=1e-4, atol=1e-3)

@@ -59,6 +59,49 @@ def worker(rank, world, port, failures):
                 failures.append(f"rank {rank}: fused K-sharded result is off (local_combine={local_combine})")
     except Exception as error:  # noqa: BLE001 - reported to the parent, the process leaves in order
         failures.append(f"rank {rank}: fused K-sharded GEMM raised {type(error).__name__}: {error}")
+    # Host operands, rows split over the ranks, B uploaded once in total: every rank sends its share of
+    # B's rows over PCIe and the ranks all-gather the rest over NVLink.
+    try:
+        import flash_train.torch as ft_torch
+
+        k_host = 8192  # divisible by every world size used here
+        host_generator = torch.Generator().manual_seed(9)
+        a_host = torch.randn(m, k_host, generator=host_generator)
+        b_host = torch.randn(k_host, n, generator=host_generator).pin_memory()
+        mine = slice(rows.start, rows.stop)
+        pipeline = ft_torch.HostGemm(rows.stop - rows.start, n, k_host, device=device, band_rows=32, group=dist.group.WORLD)
+        a_mine = a_host[mine].contiguous().pin_memory()
+        for _ in range(2):
+            d_host = pipeline(a_mine, b_host)
+            torch.cuda.synchronize()
+            expected = a_host[mine].double() @ b_host.double()
+            if not torch.allclose(d_host.double(), expected, rtol=1e-4, atol=2e-2):
+                failures.append(f"rank {rank}: HostGemm with a shared upload of B is off")
+    except Exception as error:  # noqa: BLE001
+        failures.append(f"rank {rank}: HostGemm with a process group raised {type(error).__name__}: {error}")
+    # Integer-valued operands: every product and every partial sum is exact in FP32 (|sum| < 2^24), so the
+    # fused form -- up to `world` GPUs adding into one element at the same time -- must reproduce the
+    # reduce-scatter form and the float64 product bit for bit. A lost addition cannot hide in rounding.
+    try:
+        a_int = torch.randint(-2, 3, (m, k), device=device, generator=generator).float()
+        b_int = torch.randint(-2, 3, (k, n), device=device, generator=generator).float()
+        exact_int = (a_int.double() @ b_int.double())[split.row_start:split.row_stop]
+        a_cols = a_int[:, split.k_start:split.k_stop].contiguous()
+        b_rows = b_int[split.k_start:split.k_stop].contiguous()
+        d_scattered = split(a_cols, b_rows, None, 1.0, 0.0).clone()
+        torch.cuda.synchronize()
+        if not torch.equal(d_scattered.double(), exact_int):
+            failures.append(f"rank {rank}: K-sharded integer product is not exact")
+        for local_combine in (True, False):
+            fused = sharded.FusedKShardedGemm(m, n, k, local_combine=local_combine)
+            for repeat in range(3):
+                d_fused = fused(a_cols, b_rows, None, 1.0, 0.0)
+                torch.cuda.synchronize()
+                if not torch.equal(d_fused, d_scattered):
+                    failures.append(f"rank {rank}: fused integer product differs from the reduce-scatter form "
+                                    f"(local_combine={local_combine}, call {repeat})")
+    except Exception as error:  # noqa: BLE001
+        failures.append(f"rank {rank}: integer-valued K-sharded check raised {type(error).__name__}: {error}")
     dist.barrier()
     dist.destroy_process_group()
 
@@ -68,7 +111,7 @@ def test_sharded_gemm_on_all_visible_gpus(native_library):
         pytest.fail("the GPU tests need a CUDA device")
     import torch.multiprocessing as mp
 
-    world = min(torch.cuda.device_count(), 4)
+    world = torch.cuda.device_count()  # every visible GPU (1, 2, 4 or 8 ranks; m = 512 divides)
     with socket.socket() as probe:
         probe.bind(("127.0.0.1", 0))
         port = probe.getsockname()[1]

@@ -44,10 +44,19 @@ def test_static_scratch_matches_workspace_variant_twice(capi, gpu):
         d = torch.full((m, n), float("nan"), device="cuda")
         desc = capi.make_desc(gpu.operand(a), gpu.operand(b), gpu.operand(c), gpu.operand(d), alpha, beta,
                               torch.cuda.current_device())
+        # A first call may load the kernel's module and resolve the scratch address; the check that
+        # nothing is allocated is made around a second call. torch's own counter only sees torch's
+        # caching allocator, so the driver's free-memory figure (cudaMemGetInfo) is compared as well.
+        capi.splitk_static(desc, gpu.current_stream())
+        torch.cuda.synchronize()
+        d.fill_(float("nan"))
+        torch.cuda.synchronize()
         reserved_before = torch.cuda.memory_reserved()
+        free_before = torch.cuda.mem_get_info()[0]
         capi.splitk_static(desc, gpu.current_stream())
         torch.cuda.synchronize()
         assert torch.cuda.memory_reserved() == reserved_before
+        assert torch.cuda.mem_get_info()[0] >= free_before  # an allocation inside the call would lower it
         # Both sum FP32 partial slices in order, possibly with another slice
         # count: the tolerance is the one of the exact-FP32 tests, scaled for K.
         slack = (k / 257.0) ** 0.5
