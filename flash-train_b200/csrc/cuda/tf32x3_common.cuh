@@ -72,34 +72,30 @@ __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint3
     return w;
 }
 
-// Rounds to TF32 (10 explicit mantissa bits), to nearest with ties away from
-// zero -- what cvt.rna.tf32.f32 computes -- with two full-rate integer
-// instructions: the conversion unit has a fraction of the ALU's throughput and
-// the converter warps are on the kernel's critical path. Adding half a TF32 ulp
-// to the sign-magnitude bit pattern and clearing the low 13 bits rounds the
-// magnitude. Only for values whose rounding cannot carry into the exponent
-// field 0xFF (the low part of a split, see splitTf32).
-__device__ __forceinline__ std::uint32_t tf32Round(float value) {
-    return (__float_as_uint(value) + 0x1000U) & 0xFFFFE000U;
-}
-
-// The same rounding, saturated at the largest finite TF32 magnitude (0x7F7FE000): a finite value
-// within half a TF32 ulp of FLT_MAX would otherwise round up to infinity. Infinities and NaNs also
-// come out as that finite magnitude, which is what splitTf32 wants of its high part.
+// Rounds to TF32 (10 explicit mantissa bits), to nearest with ties away from zero -- what
+// cvt.rna.tf32.f32 computes -- with integer instructions at full rate: the conversion unit has a
+// fraction of the ALU's throughput and the converter warps are on the kernel's critical path. Adding
+// half a TF32 ulp to the sign-magnitude bit pattern and clearing the low 13 bits rounds the
+// magnitude. The sum is capped at the largest finite pattern of the value's sign first: a finite
+// value within half a TF32 ulp of FLT_MAX would otherwise round up to infinity, and infinities and
+// NaNs come out as that largest finite TF32 magnitude too, which is what splitTf32 wants.
 __device__ __forceinline__ std::uint32_t tf32RoundSaturated(float value) {
     const std::uint32_t bits  = __float_as_uint(value);
-    const std::uint32_t limit = (bits & 0x80000000U) | 0x7F7FFFFFU;  // largest finite pattern of this sign
+    const std::uint32_t limit = (bits & 0x80000000U) | 0x7F7FFFFFU;
     return min(bits + 0x1000U, limit) & 0xFFFFE000U;
 }
 
-// value = hi + lo (+ a remainder below 2^-22 |value|), both TF32. The high part is always finite,
-// so the low part is exact for every finite input, FLT_MAX included. For value = +-inf the high part
-// is the largest TF32 number and the low part is +-inf, for a NaN the low part is a NaN: the three
-// products a_lo b_hi + a_hi b_lo + a_hi b_hi then give what IEEE FP32 arithmetic gives for the
-// product -- +-inf, or NaN for inf * 0 and inf - inf -- and not a NaN from inf - inf inside the split.
+// value = hi + lo: hi is value rounded to TF32 (always finite), lo the FP32 remainder value - hi,
+// which is exact for every finite value, FLT_MAX included. lo is handed to the tensor core as it is:
+// kind::tf32 reads the upper 19 bits of a 32-bit operand and ignores the rest, so the remainder is
+// truncated to TF32 by the hardware (what is cut off is below 2^-21 |value|) and no instruction is
+// spent on rounding it. For value = +-inf: hi = +-(largest TF32), lo = +-inf; for a NaN: lo = NaN.
+// The three products a_lo b_hi + a_hi b_lo + a_hi b_hi then give what IEEE FP32 arithmetic gives
+// for a b -- +-inf, or NaN for inf * 0, inf - inf and NaN operands -- instead of a NaN made inside
+// the split (inf - inf) or a NaN lost in it.
 __device__ __forceinline__ void splitTf32(float value, std::uint32_t& hi, std::uint32_t& lo) {
     hi = tf32RoundSaturated(value);
-    lo = tf32Round(value - __uint_as_float(hi));
+    lo = __float_as_uint(value - __uint_as_float(hi));
 }
 
 // Element-wise tail of writeRowSegment for outputs that cannot take 128-bit stores.
