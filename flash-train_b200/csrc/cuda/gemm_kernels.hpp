@@ -9,6 +9,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <vector>
 
 #include "ftcuda/ftcuda.h"
 
@@ -124,6 +125,33 @@ cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float
 cudaError_t launchSplitKReduceScatter(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,
                                       float* const* owner_rows, std::uint32_t owners, std::uint32_t rows_per_owner,
                                       cudaStream_t stream);
+
+// ---- grouped launches (ftcuda_grouped_gemm_*): many independent GEMMs behind one call ----
+
+// What ftcuda_grouped_gemm_configure builds (a heap object behind the opaque handle).
+struct GroupedLaunchState {
+    std::int32_t kernel = 0;
+    std::int32_t device = 0;
+    // FTCUDA_GROUPED_GEMM_EXACT: one configured launch of the exact-FP32 family per non-empty group.
+    std::vector<LaunchState> per_group;
+    // FTCUDA_GROUPED_GEMM_TF32X3: the table the persistent kernel walks -- one GroupEntry per non-empty
+    // group, then the group index of every work item -- exactly as it is copied into the workspace.
+    std::vector<unsigned char> table;
+    std::uint32_t entries = 0;
+    std::uint32_t items   = 0;
+    std::uint32_t grid    = 0;
+    std::uint32_t a_m_contiguous = 0, b_k_contiguous = 0;
+    float alpha = 0.0F, beta = 0.0F;
+    std::uint64_t workspace_bytes = 0;
+    int* device_status            = nullptr;
+    volatile int* host_status     = nullptr;
+};
+
+// The persistent tensor-core kernel over the tiles of all groups (gemm_tf32x3.cu).
+const char* supportsTensorGrouped(const FtcudaGemmDesc* groups, std::uint32_t count);
+int configureTensorGrouped(GroupedLaunchState& state, const FtcudaGemmDesc* groups, std::uint32_t count, char* message,
+                           std::size_t capacity);
+cudaError_t launchTensorGrouped(const GroupedLaunchState& state, void* workspace, cudaStream_t stream);
 
 // D = alpha * sum_s partial[s] + beta * C over `splits` dense m x n partials.
 cudaError_t launchSplitKReduce(const FtcudaGemmDesc& desc, const float* partials, std::uint32_t splits,

@@ -65,6 +65,7 @@
 
 #include <cstdint>
 #include <cstdlib>
+#include <cstring>
 
 #include "gemm_kernels.hpp"
 #include <cooperative_groups.h>
@@ -121,7 +122,9 @@ struct Barriers {
 
 // kClustered: the cluster form (K slices of a tile as a thread-block cluster) is its own
 // instantiation, so that the plain form compiles exactly as it did without it.
-template<bool kClustered>
+// kGrouped: one persistent launch over the tiles of many independent GEMMs (ftcuda_grouped_gemm_*);
+// the descriptors and output views of a work item come from its group's table entry.
+template<bool kClustered, bool kGrouped = false>
 __global__ void __launch_bounds__(kThreads, 1)
 tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const TensorParams p, const std::uint32_t num_items) {
@@ -171,7 +174,10 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
+            const ItemView view   = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+            const WorkItem& w     = view.w;
+            const void* const at_a = kGrouped ? static_cast<const void*>(&view.group->map_a) : static_cast<const void*>(&map_a);
+            const void* const at_b = kGrouped ? static_cast<const void*>(&view.group->map_b) : static_cast<const void*>(&map_b);
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t use    = it / kRawSlots;
@@ -182,16 +188,16 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (lane == 0) {
                     mbarrierArriveExpectTx(&bars->raw_full[r], kRawSlotBytes);
                     if (p.a_m_contiguous != 0) {
-                        tmaLoad2d(slot, &map_a, &bars->raw_full[r], static_cast<std::int32_t>(w.tile_m), k_coord);
+                        tmaLoad2d(slot, at_a, &bars->raw_full[r], static_cast<std::int32_t>(w.tile_m), k_coord);
                     } else {
-                        tmaLoad2d(slot, &map_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
+                        tmaLoad2d(slot, at_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
                     }
                     if (p.b_k_contiguous != 0) {
                         // One box: 192 rows (n) of 32 K values, already in the MMA's K-major layout.
-                        tmaLoad2d(slot + kRawABytes, &map_b, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_n));
+                        tmaLoad2d(slot + kRawABytes, at_b, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_n));
                     } else {
                         for (int q = 0; q < kBoxes; ++q) {
-                            tmaLoad2d(slot + kRawABytes + q * kBoxBytes, &map_b, &bars->raw_full[r],
+                            tmaLoad2d(slot + kRawABytes + q * kBoxBytes, at_b, &bars->raw_full[r],
                                       static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
                         }
                     }
@@ -210,9 +216,10 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks = 0;  // chunks started so far, over all items
         bool ok              = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
+            const ItemView view = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+            const WorkItem& w   = view.w;
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const bool chunk_start = kb % p.chunk_k_blocks == 0;
+                const bool chunk_start = kb % view.chunk_k_blocks == 0;
                 if (chunk_start) {
                     // The drain warps must have emptied the chunk accumulator.
                     ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag));
@@ -246,7 +253,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         umaTf32TmemA(tmem_base, a_hi + step * 8, b_hi + advance, kInstruction, 1U);
                     }
                     umaCommit(&bars->mma_done[s]);
-                    const bool chunk_end = (kb + 1) % p.chunk_k_blocks == 0 || kb + 1 == w.k_blocks;
+                    const bool chunk_end = (kb + 1) % view.chunk_k_blocks == 0 || kb + 1 == w.k_blocks;
                     if (chunk_end) { umaCommit(&bars->acc_full); }
                 }
                 __syncwarp();
@@ -270,7 +277,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t it = 0;
         bool ok          = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = decodeItem<kClustered>(p, item, kTileM);
+            const WorkItem w = fetchItem<kClustered, kGrouped>(p, item, kTileM).w;
             for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
                 const std::uint32_t r      = it % kRawSlots;
                 const std::uint32_t s      = it % kStages;
@@ -366,16 +373,29 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         std::uint32_t chunks          = 0;
         bool ok                       = true;
         for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w               = decodeItem<kClustered>(p, item, kTileM);
-            const std::uint32_t num_chunks = (w.k_blocks + p.chunk_k_blocks - 1) / p.chunk_k_blocks;
+            const ItemView view            = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+            const WorkItem& w              = view.w;
+            // The output of this item: the launch's, or (grouped launches) its group's.
+            TensorParams out = p;
+            if constexpr (kGrouped) {
+                out.c            = view.group->c;
+                out.d            = view.group->d;
+                out.c_row_stride = view.group->c_row_stride;
+                out.c_col_stride = view.group->c_col_stride;
+                out.d_row_stride = view.group->d_row_stride;
+                out.d_col_stride = view.group->d_col_stride;
+                out.m            = view.group->m;
+                out.n            = view.group->n;
+            }
+            const std::uint32_t num_chunks = (w.k_blocks + view.chunk_k_blocks - 1) / view.chunk_k_blocks;
             const std::uint32_t row        = w.tile_m + lane_base + lane;
-            const bool partial             = p.partials != nullptr;
-            const float* out_base = partial ? p.partials + static_cast<std::uint64_t>(w.split) * p.m * p.n : p.d;
+            const bool partial             = out.partials != nullptr;
+            const float* out_base = partial ? out.partials + static_cast<std::uint64_t>(w.split) * out.m * out.n : out.d;
             const bool vector_ok =
-                (p.n & 3) == 0 && (reinterpret_cast<std::uintptr_t>(out_base) & 15) == 0 &&
-                (partial || (p.d_col_stride == 1 && (p.d_row_stride & 3) == 0)) &&
-                (partial || p.c == nullptr ||
-                 (p.c_col_stride == 1 && (p.c_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(p.c) & 15) == 0));
+                (out.n & 3) == 0 && (reinterpret_cast<std::uintptr_t>(out_base) & 15) == 0 &&
+                (partial || (out.d_col_stride == 1 && (out.d_row_stride & 3) == 0)) &&
+                (partial || out.c == nullptr ||
+                 (out.c_col_stride == 1 && (out.c_row_stride & 3) == 0 && (reinterpret_cast<std::uintptr_t>(out.c) & 15) == 0));
             for (std::uint32_t chunk = 0; chunk < num_chunks && ok; ++chunk, ++chunks) {
                 ok = mbarrierWait(&bars->acc_full, chunks & 1, abort_flag);
                 if (!ok) { break; }
@@ -402,7 +422,7 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
                     }
                     if (last && !kClustered) {
-                        writeRowSegment(p, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
+                        writeRowSegment(out, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
                     } else {
                         tmemStore16(tmem_row + kRunningColumn + col_half + piece * 16, sum);
                     }
@@ -792,6 +812,134 @@ cudaError_t launchTensorScatter(const LaunchState& state, void* workspace, float
         ++launches;
     }
     countLaunches(launches);
+    return error;
+}
+
+// ---------------------------------------------------------------- grouped launches
+//
+// One persistent launch over the 128 x 192 tiles of all groups: the work list names the group of
+// every tile, the group's table entry carries its TMA descriptors, output views and extents. The
+// table is made once, when the launch is configured, and copied into the caller's workspace in
+// front of every launch (the workspace is the caller's between launches).
+
+namespace {
+
+constexpr std::uint64_t kTableAlignment = 128;
+
+// Layout class of a group's operands, or a reason why the tensor-core kernel cannot take it.
+const char* groupLayout(const FtcudaGemmDesc& desc, bool* a_m_contiguous, bool* b_k_contiguous) {
+    const char* reason = supportsTensor(desc, false);
+    if (reason != nullptr) { return reason; }
+    *a_m_contiguous = !tmaEligible(desc.a, desc.a_col_stride, desc.a_row_stride, desc.k, desc.m);
+    *b_k_contiguous = !tmaEligible(desc.b, desc.b_col_stride, desc.b_row_stride, desc.n, desc.k);
+    return nullptr;
+}
+
+}  // namespace
+
+const char* supportsTensorGrouped(const FtcudaGemmDesc* groups, std::uint32_t count) {
+    bool any = false, first_a = false, first_b = false;
+    std::uint64_t tiles = 0;
+    for (std::uint32_t g = 0; g < count; ++g) {
+        const FtcudaGemmDesc& desc = groups[g];
+        if (desc.m * desc.n == 0) { continue; }  // an empty group has no tiles
+        bool a_m = false, b_k = false;
+        const char* reason = groupLayout(desc, &a_m, &b_k);
+        if (reason != nullptr) { return reason; }
+        if (any && (a_m != first_a || b_k != first_b)) { return "the groups do not share one operand layout (row-major or transposed view)"; }
+        if (!any) { first_a = a_m, first_b = b_k, any = true; }
+        tiles += ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
+        if (tiles >= (1ULL << 24)) { return "too many output tiles"; }
+    }
+    if (!any) { return "every group is empty"; }
+    return nullptr;
+}
+
+int configureTensorGrouped(GroupedLaunchState& state, const FtcudaGemmDesc* groups, std::uint32_t count, char* message,
+                           std::size_t capacity) {
+    int sms = 0;
+    if (!deviceSmCount(state.device, &sms, message, capacity)) { return 1; }
+    if (!deviceStatusWord(state.device, &state.device_status, &state.host_status, message, capacity)) { return 1; }
+    std::vector<GroupEntry> entries;
+    std::vector<std::uint32_t> item_group;
+    const std::uint32_t band = bandMTiles();
+    for (std::uint32_t g = 0; g < count; ++g) {
+        const FtcudaGemmDesc& desc = groups[g];
+        if (desc.m * desc.n == 0) { continue; }
+        bool a_m = false, b_k = false;
+        if (const char* reason = groupLayout(desc, &a_m, &b_k)) { return fail(message, capacity, 1, "group %u: %s", g, reason); }
+        state.a_m_contiguous = a_m ? 1U : 0U;
+        state.b_k_contiguous = b_k ? 1U : 0U;
+        GroupEntry entry{};
+        const bool a_encoded =
+            !a_m ? encodeTensorMap2d(&entry.map_a, desc.a, desc.k, desc.m, static_cast<std::uint64_t>(desc.a_row_stride) * sizeof(float),
+                                     kTileK, kTileM, true, message, capacity)
+                 : encodeTensorMap2d(&entry.map_a, desc.a, desc.m, desc.k, static_cast<std::uint64_t>(desc.a_col_stride) * sizeof(float),
+                                     kTileM, kTileK, false, message, capacity);
+        if (!a_encoded) { return 1; }
+        const bool b_encoded =
+            !b_k ? encodeTensorMap2d(&entry.map_b, desc.b, desc.n, desc.k, static_cast<std::uint64_t>(desc.b_row_stride) * sizeof(float), 32,
+                                     kTileK, kSwizzle128Atom32, message, capacity)
+                 : encodeTensorMap2d(&entry.map_b, desc.b, desc.k, desc.n, static_cast<std::uint64_t>(desc.b_col_stride) * sizeof(float),
+                                     kTileK, kTileN, kSwizzle128, message, capacity);
+        if (!b_encoded) { return 1; }
+        entry.c              = desc.c;
+        entry.d              = desc.d;
+        entry.c_row_stride   = desc.c_row_stride;
+        entry.c_col_stride   = desc.c_col_stride;
+        entry.d_row_stride   = desc.d_row_stride;
+        entry.d_col_stride   = desc.d_col_stride;
+        entry.m              = static_cast<std::uint32_t>(desc.m);
+        entry.n              = static_cast<std::uint32_t>(desc.n);
+        entry.k              = static_cast<std::uint32_t>(desc.k);
+        entry.chunk_k_blocks = chunkKBlocks(desc.k);
+        entry.first_item     = static_cast<std::uint32_t>(item_group.size());
+        entry.tiles_m        = static_cast<std::uint32_t>(ceilDiv(desc.m, kTileM));
+        entry.tiles_n        = static_cast<std::uint32_t>(ceilDiv(desc.n, kTileN));
+        entry.band_m_tiles   = band;
+        item_group.insert(item_group.end(), static_cast<std::size_t>(entry.tiles_m) * entry.tiles_n,
+                          static_cast<std::uint32_t>(entries.size()));
+        entries.push_back(entry);
+        state.alpha = desc.alpha;
+        state.beta  = desc.beta;
+    }
+    state.entries = static_cast<std::uint32_t>(entries.size());
+    state.items   = static_cast<std::uint32_t>(item_group.size());
+    state.grid    = state.items < static_cast<std::uint32_t>(sms) ? state.items : static_cast<std::uint32_t>(sms);
+    const std::size_t entry_bytes = entries.size() * sizeof(GroupEntry);
+    state.table.assign(entry_bytes + item_group.size() * sizeof(std::uint32_t), 0);
+    if (!state.table.empty()) {  // (vectors of size zero have no data pointer worth passing to memcpy)
+        std::memcpy(state.table.data(), entries.data(), entry_bytes);
+        std::memcpy(state.table.data() + entry_bytes, item_group.data(), item_group.size() * sizeof(std::uint32_t));
+    }
+    // Room to place the table at a 128-byte boundary whatever the workspace's own alignment is.
+    state.workspace_bytes = state.table.size() + kTableAlignment;
+    const cudaError_t error =
+        cudaFuncSetAttribute(tensorGemm3xTf32<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (error != cudaSuccess) { return fail(message, capacity, 1, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(error)); }
+    return 0;
+}
+
+cudaError_t launchTensorGrouped(const GroupedLaunchState& state, void* workspace, cudaStream_t stream) {
+    if (state.items == 0) { return cudaSuccess; }
+    const std::uintptr_t aligned = (reinterpret_cast<std::uintptr_t>(workspace) + kTableAlignment - 1) & ~(kTableAlignment - 1);
+    unsigned char* table         = reinterpret_cast<unsigned char*>(aligned);
+    cudaError_t error = cudaMemcpyAsync(table, state.table.data(), state.table.size(), cudaMemcpyHostToDevice, stream);
+    if (error != cudaSuccess) { return error; }
+    TensorParams p{};
+    p.splits         = 1;
+    p.a_m_contiguous = state.a_m_contiguous;
+    p.b_k_contiguous = state.b_k_contiguous;
+    p.alpha          = state.alpha;
+    p.beta           = state.beta;
+    p.status         = state.device_status;
+    p.groups         = reinterpret_cast<const GroupEntry*>(table);
+    p.item_group     = reinterpret_cast<const std::uint32_t*>(table + static_cast<std::size_t>(state.entries) * sizeof(GroupEntry));
+    // The descriptor arguments of the ordinary form are unused here: every item takes its group's.
+    const CUtensorMap unused{};
+    tensorGemm3xTf32<false, true><<<state.grid, kThreads, kSmemBytes, stream>>>(unused, unused, p, state.items);
+    error = cudaGetLastError();
+    countLaunches(1);
     return error;
 }
 

@@ -3,6 +3,7 @@
 // epilogue's row-segment writer.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -20,6 +21,8 @@ inline std::uint32_t drainInterval(std::uint64_t k) {
     while (blocks < 16 && static_cast<std::uint64_t>(blocks + 1) * (blocks + 1) * 156 <= k) { ++blocks; }  // 12.5^2 = 156.25
     return blocks;
 }
+
+struct GroupEntry;
 
 struct TensorParams {
     const float* c;
@@ -44,7 +47,29 @@ struct TensorParams {
     // cluster_ranks + slice, one work item per CTA) and meet through distributed shared memory.
     std::uint32_t cluster_ranks;
     int* status;
+    // Grouped launches: the per-group table and, per work item, the index of its group.
+    const GroupEntry* groups;
+    const std::uint32_t* item_group;
 };
+
+// Grouped launches (one persistent launch over the output tiles of many independent GEMMs): one
+// entry per group in device memory, followed by the list that names the group of every work item.
+// The entry holds what differs from group to group -- the two TMA descriptors, the output views and
+// the extents --; alpha, beta and the operands' layout class are those of the launch.
+struct alignas(128) GroupEntry {
+    CUtensorMap map_a;
+    CUtensorMap map_b;
+    const float* c;
+    float* d;
+    std::int64_t c_row_stride, c_col_stride;
+    std::int64_t d_row_stride, d_col_stride;
+    std::uint32_t m, n, k;
+    std::uint32_t chunk_k_blocks;
+    std::uint32_t first_item;  // index of the group's first work item in the launch's list
+    std::uint32_t tiles_m, tiles_n;
+    std::uint32_t band_m_tiles;
+};
+static_assert(sizeof(GroupEntry) % 128 == 0, "entries are laid out back to back at 128-byte boundaries");
 
 struct WorkItem {
     std::uint32_t tile_m, tile_n;  // element offsets
@@ -70,6 +95,39 @@ __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint3
     const std::uint32_t k_end = min(p.k, w.k_begin + p.k_per_split);
     w.k_blocks                = (k_end - w.k_begin + kTileK - 1) / kTileK;
     return w;
+}
+
+// One work item as a role of the kernel needs it: where the tile is, how deep K is, how often the
+// accumulator is drained, and (grouped launches) the group's table entry.
+struct ItemView {
+    WorkItem w;
+    std::uint32_t chunk_k_blocks;
+    const GroupEntry* group;  // null for an ordinary launch
+};
+
+template<bool kClustered, bool kGrouped>
+__device__ __forceinline__ ItemView fetchItem(const TensorParams& p, std::uint32_t item, std::uint32_t tile_rows) {
+    ItemView view;
+    if constexpr (kGrouped) {
+        const GroupEntry* group   = p.groups + p.item_group[item];
+        const std::uint32_t tile  = item - group->first_item;
+        const std::uint32_t band  = tile / (group->band_m_tiles * group->tiles_n);
+        const std::uint32_t first = band * group->band_m_tiles;
+        const std::uint32_t rows  = min(group->band_m_tiles, group->tiles_m - first);
+        const std::uint32_t rest  = tile - band * group->band_m_tiles * group->tiles_n;
+        view.w.tile_m             = (first + rest % rows) * tile_rows;
+        view.w.tile_n             = (rest / rows) * kTileN;
+        view.w.split              = 0;
+        view.w.k_begin            = 0;
+        view.w.k_blocks           = (group->k + kTileK - 1) / kTileK;
+        view.chunk_k_blocks       = group->chunk_k_blocks;
+        view.group                = group;
+    } else {
+        view.w              = decodeItem<kClustered>(p, item, tile_rows);
+        view.chunk_k_blocks = p.chunk_k_blocks;
+        view.group          = nullptr;
+    }
+    return view;
 }
 
 // Rounds to TF32 (10 explicit mantissa bits), to nearest with ties away from zero -- what

@@ -24,6 +24,7 @@ STATUS_UNSUPPORTED = 4
 STATUS_INTERNAL_ERROR = 50
 
 NUMERIC_FP64 = 1
+NUMERIC_INT64 = 2
 NUMERIC_FP32 = 4
 NUMERIC_FP16 = 7
 NUMERIC_COUNT = 24
@@ -50,7 +51,9 @@ PLATFORM_SYMBOLS = (
     "ftcuda_current_device ftcuda_device_sm_count ftcuda_gemm_supports ftcuda_gemm_configure "
     "ftcuda_gemm_workspace_bytes ftcuda_gemm_launch ftcuda_launch_count ftcuda_trace_push ftcuda_trace_pop "
     "ftcuda_trace_mark ftcuda_gemm_splitk_static ftcuda_gemm_splitk_static_capacity ftcuda_gemm_launch_scatter "
-    "ftcuda_device_status ftcuda_device_status_reset ftcuda_selftest_bounded_wait ftcuda_measure_ffma_tflops"
+    "ftcuda_device_status ftcuda_device_status_reset ftcuda_selftest_bounded_wait ftcuda_measure_ffma_tflops "
+    "ftcuda_grouped_gemm_supports ftcuda_grouped_gemm_configure ftcuda_grouped_gemm_workspace_bytes "
+    "ftcuda_grouped_gemm_launch ftcuda_grouped_gemm_destroy"
 ).split()
 
 
@@ -248,6 +251,19 @@ class Args(_Handle):
     def set_gemm(self, op: RoleId, compute_type: int = NUMERIC_FP32) -> None:
         self.check(self.lib.ftrainArgsSetGemm(self.handle, op, compute_type))
 
+    def set_grouped_tensor(self, role: RoleId, num_groups: int, data: StorageView, offsets=None, dim_sizes=None,
+                           strides=None) -> None:
+        """offsets: one StorageView or None; dim_sizes / strides: a sequence of data.num_dims StorageViews or None."""
+        def array(views):
+            return (StorageView * len(views))(*views) if views is not None else None
+
+        self.check(self.lib.ftrainArgsSetGroupedTensor(self.handle, role, num_groups, data,
+                                                       byref(offsets) if offsets is not None else None,
+                                                       array(dim_sizes), array(strides)))
+
+    def set_grouped_abcd_gemm(self, op: RoleId, compute_type: int = NUMERIC_FP32) -> None:
+        self.check(self.lib.ftrainArgsSetGroupedABCDGemm(self.handle, op, compute_type))
+
 
 class Plan(_Handle):
     _destroy = "ftrainPlanDestroy"
@@ -318,6 +334,57 @@ class GemmBinding:
     def make_plan(self, a, b, c, d, alpha: float = 1.0, beta: float = 0.0) -> Plan:
         """alpha and beta are read during this call; the Args can go afterwards."""
         args, keep = self.make_args(a, b, c, d, alpha, beta)
+        plan = Plan(args)
+        args.close()
+        del keep
+        return plan
+
+
+class GroupedGemmBinding:
+    """Pattern -> Ops for the GroupedABCDGemm graph (four GroupedTensors, two scalars), plus a Plan factory.
+
+    A grouped operand is given as (address of the data, rows per group, columns per group) with
+    optional per-group element offsets and (row, column) element strides; without them the groups
+    are dense row-major matrices stored one after another. The per-group arrays are passed to the
+    library as int64 host arrays, which it reads while the Plan is made.
+    """
+
+    def __init__(self, order=("a", "b", "c", "alpha", "beta", "d"), lib=lib):
+        pattern = Pattern(lib)
+        grouped = {"a", "b", "c", "d"}
+        self.roles = {name: (pattern.add_grouped_tensor() if name in grouped else pattern.add_tensor()) for name in order}
+        r = self.roles
+        self.gemm = pattern.add_gemm(r["a"], r["b"], r["c"], r["d"], r["alpha"], r["beta"], kind="GroupedABCDGemm")
+        self.ops = Ops(pattern)
+        pattern.close()
+
+    def make_plan(self, a, b, c, d, alpha: float = 1.0, beta: float = 0.0, compute_type: int = NUMERIC_FP32) -> "Plan":
+        """a, b, c, d: dicts with keys address, rows, cols and optionally offsets, row_strides, col_strides."""
+        args = Args(self.ops)
+        keep = []
+
+        def vector(values):
+            array = (c_int64 * max(len(values), 1))(*values)
+            view, alive = make_view(ctypes.addressof(array), (len(values),), numeric_type=NUMERIC_INT64, host=True)
+            keep.extend((array, alive))
+            return view
+
+        for name, operand in (("a", a), ("b", b), ("c", c), ("d", d)):
+            groups = len(operand["rows"])
+            data, alive = make_view(operand["address"], (0, 0), index_type=INDEX_GROUPED_CONTINUOUS)
+            keep.append(alive)
+            dims = [vector(operand["rows"]), vector(operand["cols"])]
+            offsets = vector(operand["offsets"]) if operand.get("offsets") is not None else None
+            strides = ([vector(operand["row_strides"]), vector(operand["col_strides"])]
+                       if operand.get("row_strides") is not None else None)
+            args.set_grouped_tensor(self.roles[name], groups, data, offsets, dims, strides)
+        scalars = (ctypes.c_float * 2)(alpha, beta)
+        keep.append(scalars)
+        for index, name in enumerate(("alpha", "beta")):
+            view, alive = make_view(ctypes.addressof(scalars) + 4 * index, (), host=True)
+            keep.append(alive)
+            args.set_tensor(self.roles[name], view)
+        args.set_grouped_abcd_gemm(self.gemm, compute_type)
         plan = Plan(args)
         args.close()
         del keep

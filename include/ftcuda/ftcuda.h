@@ -156,6 +156,37 @@ FTCUDA_API int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* 
                                           char* message, size_t message_capacity);
 
 /*
+ * Grouped GEMM: D_g = alpha * A_g * B_g + beta * C_g for num_groups independent problems, each given
+ * as an ordinary descriptor (alpha, beta and device equal in all of them). The reference declares the
+ * operation in its public API (include/flash_train/common.h:248-266 there) but ships no Primitive for
+ * it; these entry points are what this build's GroupedABCDGemm Primitives stand on. Groups with
+ * m * n == 0 are skipped.
+ *   FTCUDA_GROUPED_GEMM_EXACT   exact FP32 (FFMA): one launch of the FTCUDA_GEMM_SIMT family per
+ *                               non-empty group; any layout, K = 0 included; no workspace.
+ *   FTCUDA_GROUPED_GEMM_TF32X3  one persistent launch of the 3xTF32 tensor-core kernel over the
+ *                               output tiles of all groups. Every non-empty group must suit
+ *                               FTCUDA_GEMM_TF32X3 (K >= 128, TMA-eligible A and B) and all groups
+ *                               must share one operand layout class. The per-group table (TMA
+ *                               descriptors, output views) is copied into the workspace by every
+ *                               launch: ftcuda_grouped_gemm_workspace_bytes says how large it is.
+ * configure returns a heap object through *launch; destroy frees it (NULL is allowed).
+ */
+enum {
+    FTCUDA_GROUPED_GEMM_EXACT        = 0,
+    FTCUDA_GROUPED_GEMM_TF32X3       = 1,
+    FTCUDA_GROUPED_GEMM_KERNEL_COUNT = 2,
+};
+typedef struct FtcudaGroupedGemmLaunch FtcudaGroupedGemmLaunch;
+FTCUDA_API int ftcuda_grouped_gemm_supports(int kernel, const FtcudaGemmDesc* groups, uint32_t num_groups, char* message,
+                                            size_t message_capacity);
+FTCUDA_API int ftcuda_grouped_gemm_configure(int kernel, const FtcudaGemmDesc* groups, uint32_t num_groups,
+                                             FtcudaGroupedGemmLaunch** launch, char* message, size_t message_capacity);
+FTCUDA_API uint64_t ftcuda_grouped_gemm_workspace_bytes(const FtcudaGroupedGemmLaunch* launch);
+FTCUDA_API int ftcuda_grouped_gemm_launch(const FtcudaGroupedGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                          void* stream, char* message, size_t message_capacity);
+FTCUDA_API void ftcuda_grouped_gemm_destroy(FtcudaGroupedGemmLaunch* launch);
+
+/*
  * Per-device status word (no counterpart in the reference, whose kernel has no device-side waits).
  * Every wait inside the kernels is bounded; a kernel whose wait ran out stops its pipeline, frees
  * its tensor memory, returns, and leaves a nonzero code in a word of mapped host memory. The next

@@ -2,6 +2,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 namespace fake {
 
@@ -99,6 +100,61 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
     const auto* blob = reinterpret_cast<const fake::Blob*>(launch);
     fake::state().launches.push_back(fake::LaunchRecord{blob->kernel, workspace, workspace_bytes, stream, blob->desc});
     return 0;
+}
+
+// ---- grouped entry points: the same rules as the real layer, nothing launched ----
+struct FtcudaGroupedGemmLaunch {
+    int kernel;
+    std::uint64_t workspace;
+    std::vector<FtcudaGemmDesc> groups;
+};
+
+extern "C" int ftcuda_grouped_gemm_supports(int kernel, const FtcudaGemmDesc* groups, uint32_t num_groups, char* message,
+                                            size_t capacity) {
+    ++fake::state().supports;
+    if (kernel == FTCUDA_GROUPED_GEMM_EXACT) { return 0; }
+    if (kernel != FTCUDA_GROUPED_GEMM_TF32X3) { return fake::fail(message, capacity, "unknown grouped kernel family"); }
+    bool any = false;
+    for (uint32_t g = 0; g < num_groups; ++g) {
+        if (groups[g].m * groups[g].n == 0) { continue; }
+        any = true;
+        if (ftcuda_gemm_supports(FTCUDA_GEMM_TF32X3, &groups[g], message, capacity) != 0) { return 1; }
+        if (groups[g].k < 128) { return fake::fail(message, capacity, "K is too short for the split-precision kernel (under 128)"); }
+    }
+    return any ? 0 : fake::fail(message, capacity, "every group is empty");
+}
+
+extern "C" int ftcuda_grouped_gemm_configure(int kernel, const FtcudaGemmDesc* groups, uint32_t num_groups,
+                                             FtcudaGroupedGemmLaunch** launch, char* message, size_t capacity) {
+    ++fake::state().configures;
+    if (const char* reason = fake::state().fail_next_configure) {
+        fake::state().fail_next_configure = nullptr;
+        return fake::fail(message, capacity, reason);
+    }
+    auto* made      = new FtcudaGroupedGemmLaunch{};
+    made->kernel    = kernel;
+    made->workspace = kernel == FTCUDA_GROUPED_GEMM_TF32X3 ? fake::state().grouped_tensor_workspace : 0;
+    made->groups.assign(groups, groups + num_groups);
+    ++fake::state().grouped_live;
+    *launch = made;
+    return 0;
+}
+
+extern "C" uint64_t ftcuda_grouped_gemm_workspace_bytes(const FtcudaGroupedGemmLaunch* launch) { return launch->workspace; }
+
+extern "C" int ftcuda_grouped_gemm_launch(const FtcudaGroupedGemmLaunch* launch, void* workspace, uint64_t workspace_bytes,
+                                          void* stream, char* message, size_t capacity) {
+    if (const char* reason = fake::state().fail_next_launch) {
+        fake::state().fail_next_launch = nullptr;
+        return fake::fail(message, capacity, reason);
+    }
+    fake::state().grouped_launches.push_back(fake::GroupedLaunchRecord{launch->kernel, workspace, workspace_bytes, stream, launch->groups});
+    return 0;
+}
+
+extern "C" void ftcuda_grouped_gemm_destroy(FtcudaGroupedGemmLaunch* launch) {
+    if (launch != nullptr) { --fake::state().grouped_live; }
+    delete launch;
 }
 
 extern "C" uint64_t ftcuda_launch_count(void) { return fake::state().launches.size(); }

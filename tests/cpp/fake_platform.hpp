@@ -21,12 +21,23 @@ struct LaunchRecord {
     FtcudaGemmDesc desc;
 };
 
+struct GroupedLaunchRecord {
+    int kernel;
+    void* workspace;
+    std::uint64_t workspace_bytes;
+    void* stream;
+    std::vector<FtcudaGemmDesc> groups;
+};
+
 struct State {
     int device               = 0;
     bool device_query_fails  = false;
     int sm_count             = 148;
     std::uint64_t split_k_workspace = 4096;  // what the fake split-K kernels ask for
     std::vector<LaunchRecord> launches;
+    std::vector<GroupedLaunchRecord> grouped_launches;
+    std::uint64_t grouped_tensor_workspace = 1024;  // what the fake grouped tensor-core kernel asks for
+    int grouped_live = 0;                           // configured grouped launches not yet destroyed
     int configures = 0;
     int supports   = 0;
     // Host-side failure injection: the next configure / launch call answers with this reason (and

@@ -96,19 +96,22 @@ TEST(ops_create_validates_and_matches) {
     CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, bad)), static_cast<int>(FTRAIN_STATUS_INVALID_ARGUMENT));
     CHECK(ops == nullptr);
     ftrainPatternDestroy(bad);
-    // A graph no engine supports: UNSUPPORTED, the caller's variable unchanged.
-    FTrainPattern grouped = nullptr;
-    ftrainPatternCreate(&grouped);
-    FTrainGroupedTensorId g[4];
-    for (auto& id : g) { ftrainPatternAddGroupedTensor(grouped, &id); }
+    // A graph no engine supports (a grouped GEMM whose c and d are TensorLists has none, here as in the
+    // reference): UNSUPPORTED, the caller's variable unchanged.
+    FTrainPattern unsupported = nullptr;
+    ftrainPatternCreate(&unsupported);
+    FTrainGroupedTensorId g[2];
+    for (auto& id : g) { ftrainPatternAddGroupedTensor(unsupported, &id); }
+    FTrainTensorListId lists[2];
+    for (auto& id : lists) { ftrainPatternAddTensorList(unsupported, &id); }
     FTrainTensorId alpha, beta;
-    ftrainPatternAddTensor(grouped, &alpha);
-    ftrainPatternAddTensor(grouped, &beta);
-    FTrainGroupedABCDGemmOpId grouped_op;
-    CHECK_EQ(static_cast<int>(ftrainPatternAddGroupedABCDGemm(grouped, &grouped_op, g[0], g[1], g[2], g[3], alpha, beta)), 0);
-    CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, grouped)), static_cast<int>(FTRAIN_STATUS_UNSUPPORTED));
+    ftrainPatternAddTensor(unsupported, &alpha);
+    ftrainPatternAddTensor(unsupported, &beta);
+    FTrainGroupedABGemmOpId list_op;
+    CHECK_EQ(static_cast<int>(ftrainPatternAddGroupedABGemm(unsupported, &list_op, g[0], g[1], lists[0], lists[1], alpha, beta)), 0);
+    CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, unsupported)), static_cast<int>(FTRAIN_STATUS_UNSUPPORTED));
     CHECK(ops == nullptr);
-    ftrainPatternDestroy(grouped);
+    ftrainPatternDestroy(unsupported);
     // The Gemm graph in a foreign insertion order matches; the Pattern can go right away.
     GemmGraph graph = makeGraph();
     CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, graph.pattern)), 0);

@@ -89,10 +89,12 @@ def api_script(capi, lib):
     record("add out of range", lambda: out_of_range.add_gemm(t[0], t[1], t[2], capi.RoleId(40), t[3], t[4]))
     record("ops(out of range)", lambda: capi.Ops(out_of_range))
 
+    # A grouped GEMM with TensorList outputs has no engine on either side.
     grouped = capi.Pattern(lib)
-    g = [grouped.add_grouped_tensor() for _ in range(4)]
+    g = [grouped.add_grouped_tensor() for _ in range(2)]
+    lists = [grouped.add_tensor_list() for _ in range(2)]
     alpha, beta = grouped.add_tensor(), grouped.add_tensor()
-    record("add grouped", lambda: grouped.add_gemm(g[0], g[1], g[2], g[3], alpha, beta, kind="GroupedABCDGemm"))
+    record("add grouped", lambda: grouped.add_gemm(g[0], g[1], lists[0], lists[1], alpha, beta, kind="GroupedABGemm"))
     record("ops(grouped: no engine)", lambda: capi.Ops(grouped))
 
     for order in (("a", "b", "c", "alpha", "beta", "d"), ("d", "c", "b", "a", "beta", "alpha")):
@@ -149,6 +151,25 @@ def test_same_statuses_as_the_reference_build(capi, reference_capi):
         assert int(lib.ftrainPatternCreate(None)) == capi.STATUS_INVALID_ARGUMENT
         assert capi.last_message(lib) == "ftrainPatternCreate: pattern output must not be null"
         assert capi.last_status(lib) == capi.STATUS_INVALID_ARGUMENT
+
+
+def test_grouped_abcd_gemm_has_an_engine_here(capi, reference_capi):
+    """The one place where this library answers differently from the reference on purpose: the
+    GroupedABCDGemm graph (declared by the reference's public header, without an engine there) matches."""
+    def ops_status(lib):
+        pattern = capi.Pattern(lib)
+        g = [pattern.add_grouped_tensor() for _ in range(4)]
+        alpha, beta = pattern.add_tensor(), pattern.add_tensor()
+        pattern.add_gemm(g[0], g[1], g[2], g[3], alpha, beta, kind="GroupedABCDGemm")
+        try:
+            capi.Ops(pattern)
+            return capi.STATUS_SUCCESS
+        except capi.FTrainError as error:
+            return error.status
+
+    assert ops_status(capi.lib) == capi.STATUS_SUCCESS
+    if reference_capi is not None:
+        assert ops_status(reference_capi) == capi.STATUS_UNSUPPORTED
 
 
 def test_plan_creation_without_a_device_fails_loudly(capi):

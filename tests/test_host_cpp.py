@@ -49,7 +49,7 @@ def test_binary():
                                    "key_", "symmetric", "matching_", "ops_rejects", "cache_", "name_lists", "engine_",
                                    "create_plan", "problem_", "fp32_gemm_checklist", "configured_clone", "plan_dispatches",
                                    "finder_", "builtin_", "role_ids", "null_arguments", "ops_create", "args_setters",
-                                   "tensor_list", "last_status", "one_shot"])
+                                   "tensor_list", "last_status", "one_shot", "grouped_"])
 def test_cpp_group(test_binary, group):
     result = subprocess.run([str(test_binary), group], capture_output=True, text=True, timeout=300)
     assert result.returncode == 0, result.stdout[-4000:] + result.stderr[-2000:]
