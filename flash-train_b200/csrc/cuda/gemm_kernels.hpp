@@ -20,6 +20,7 @@ enum Variant : int {
     kVariantGeneric  = 0,  // predicated loads, any strides (SIMT only)
     kVariantTmaAk    = 1,  // TMA; A rows contiguous along K (row-major A)
     kVariantTmaAm    = 2,  // TMA; A contiguous along M (transposed view of a K x M buffer)
+    kVariantSmall    = 3,  // SIMT only: 32 x 32 tiles with register prefetch, for outputs too small to fill the SMs otherwise
     kVariantMaskA    = 15,
     kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
     kVariantFlagPair = 32,  // tensor kernel: CTA pairs on 256-row tiles

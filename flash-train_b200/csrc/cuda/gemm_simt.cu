@@ -16,7 +16,12 @@
 //   * simtGemmGeneric: 64x64 tile with predicated scalar loads; takes any
 //     strides, any alignment, tiny shapes and K == 0. It is the path for
 //     layouts TMA cannot describe.
-// Both can restrict themselves to one K slice (blockIdx.z) and write the raw
+//   * simtGemmSmall: 32x32 tile, 128 threads, the next K block's operands
+//     fetched into registers while the current one is multiplied. For outputs so
+//     small that the larger tiles would leave most SMs idle (64^3 ... 256^3, the
+//     128x64x96 default): sixteen times as many CTAs as the 128x128 tiling, each
+//     with a short K loop whose global-memory latency is hidden. Any strides.
+// All can restrict themselves to one K slice (blockIdx.z) and write the raw
 // partial tile to a workspace, which the split-K reduction finishes.
 #include <cuda_runtime.h>
 
@@ -371,6 +376,89 @@ __global__ void __launch_bounds__(256) simtGemmGeneric(const GenericParams g) {
     }
 }
 
+// ---- small outputs: 32 x 32 tiles, 128 threads, 2 x 4 outputs per thread ----
+constexpr int kSmallTile    = 32;
+constexpr int kSmallK       = 32;
+constexpr int kSmallThreads = 128;
+
+__global__ void __launch_bounds__(kSmallThreads) simtGemmSmall(const GenericParams g) {
+    // [k][m] and [k][n], rows padded so that the transposing stores of A do not collide.
+    __shared__ float a_tile[kSmallK][kSmallTile + 1];
+    __shared__ __align__(16) float b_tile[kSmallK][kSmallTile];
+    const SimtParams& p = g.out;
+    const int tid       = threadIdx.x;
+    const int tx        = tid & 7;    // 8 column groups of 4
+    const int ty        = tid >> 3;   // 16 row groups of 2
+    const std::uint32_t tile_m  = blockIdx.y * kSmallTile;
+    const std::uint32_t tile_n  = blockIdx.x * kSmallTile;
+    const std::uint32_t k_begin = blockIdx.z * p.k_per_split;
+    const std::uint32_t k_end   = min(p.k, k_begin + p.k_per_split);
+
+    // Per K block a thread fetches 8 elements of A and 8 of B. A: consecutive threads walk K within
+    // a row when rows are contiguous along K, M otherwise (so that the loads of a warp coalesce for
+    // either layout); B: consecutive threads walk N, or K when B is contiguous along K.
+    const bool a_along_k = g.a_col_stride == 1;
+    const bool b_along_n = g.b_col_stride == 1;
+    float a_next[8];
+    float b_next[8];
+    auto fetch = [&](std::uint32_t k0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int index         = tid + e * kSmallThreads;       // 0 .. 1023
+            const int a_k           = a_along_k ? (index & 31) : (index >> 5);
+            const int a_m           = a_along_k ? (index >> 5) : (index & 31);
+            const std::uint32_t row = tile_m + a_m;
+            const std::uint32_t kk  = k0 + a_k;
+            a_next[e] = (row < p.m && kk < k_end)
+                            ? g.a[static_cast<std::int64_t>(row) * g.a_row_stride + static_cast<std::int64_t>(kk) * g.a_col_stride]
+                            : 0.0F;
+            const int b_n            = b_along_n ? (index & 31) : (index >> 5);
+            const int b_k            = b_along_n ? (index >> 5) : (index & 31);
+            const std::uint32_t col  = tile_n + b_n;
+            const std::uint32_t kk_b = k0 + b_k;
+            b_next[e] = (col < p.n && kk_b < k_end)
+                            ? g.b[static_cast<std::int64_t>(kk_b) * g.b_row_stride + static_cast<std::int64_t>(col) * g.b_col_stride]
+                            : 0.0F;
+        }
+    };
+    auto park = [&]() {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int index = tid + e * kSmallThreads;
+            a_tile[a_along_k ? (index & 31) : (index >> 5)][a_along_k ? (index >> 5) : (index & 31)] = a_next[e];
+            b_tile[b_along_n ? (index >> 5) : (index & 31)][b_along_n ? (index & 31) : (index >> 5)] = b_next[e];
+        }
+    };
+
+    float acc[2][4] = {};
+    if (k_begin < k_end) { fetch(k_begin); }
+    for (std::uint32_t k0 = k_begin; k0 < k_end; k0 += kSmallK) {
+        park();
+        __syncthreads();
+        if (k0 + kSmallK < k_end) { fetch(k0 + kSmallK); }  // in flight while this block is multiplied
+#pragma unroll
+        for (int kk = 0; kk < kSmallK; ++kk) {
+            const float a0     = a_tile[kk][ty * 2];
+            const float a1     = a_tile[kk][ty * 2 + 1];
+            const float4 b_row = *reinterpret_cast<const float4*>(&b_tile[kk][tx * 4]);
+            acc[0][0] = fmaf(a0, b_row.x, acc[0][0]);
+            acc[0][1] = fmaf(a0, b_row.y, acc[0][1]);
+            acc[0][2] = fmaf(a0, b_row.z, acc[0][2]);
+            acc[0][3] = fmaf(a0, b_row.w, acc[0][3]);
+            acc[1][0] = fmaf(a1, b_row.x, acc[1][0]);
+            acc[1][1] = fmaf(a1, b_row.y, acc[1][1]);
+            acc[1][2] = fmaf(a1, b_row.z, acc[1][2]);
+            acc[1][3] = fmaf(a1, b_row.w, acc[1][3]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { storeElement(p, tile_m + ty * 2 + i, tile_n + tx * 4 + j, acc[i][j]); }
+    }
+}
+
 SimtParams makeOutputParams(const LaunchState& state, void* workspace) {
     const FtcudaGemmDesc& desc = state.desc;
     SimtParams p{};
@@ -421,14 +509,26 @@ int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t c
     const bool large = desc.m >= 96 && desc.n >= 96 && desc.k >= 32;
     state.variant    = kVariantGeneric;
     if (b_ok && large && (a_k || a_m)) { state.variant = (a_k ? kVariantTmaAk : kVariantTmaAm) | (b_k ? kVariantFlagBk : 0); }
+    // Small outputs: the tiling above would occupy a handful of SMs with long serial K loops (one CTA
+    // for 128^3). 32 x 32 tiles put sixteen times as many CTAs to work; used while they still fit one
+    // wave with room to spare and the whole-K loop of a tile stays short. (Split-K launches keep the
+    // larger tiles: they are chosen for long K.)
+    const std::uint64_t small_tiles = ceilDiv(desc.m, kSmallTile) * ceilDiv(desc.n, kSmallTile);
+    const std::uint64_t tiles_now   = state.variant == kVariantGeneric ? ceilDiv(desc.m, kGenericTile) * ceilDiv(desc.n, kGenericTile)
+                                                                       : ceilDiv(desc.m, kTileM) * ceilDiv(desc.n, kTileN);
+    if (!split_k && desc.k > 0 && desc.k <= 1024 && tiles_now * 4 <= static_cast<std::uint64_t>(sms) &&
+        small_tiles <= 2ULL * static_cast<std::uint64_t>(sms)) {
+        state.variant = kVariantSmall;
+    }
 
-    const std::uint32_t tile_m = state.variant == kVariantGeneric ? kGenericTile : kTileM;
-    const std::uint32_t tile_n = state.variant == kVariantGeneric ? kGenericTile : kTileN;
-    const std::uint32_t tile_k = state.variant == kVariantGeneric ? kGenericK : kTileK;
+    const bool small           = state.variant == kVariantSmall;
+    const std::uint32_t tile_m = small ? kSmallTile : state.variant == kVariantGeneric ? kGenericTile : kTileM;
+    const std::uint32_t tile_n = small ? kSmallTile : state.variant == kVariantGeneric ? kGenericTile : kTileN;
+    const std::uint32_t tile_k = small ? kSmallK : state.variant == kVariantGeneric ? kGenericK : kTileK;
     state.grid_x               = static_cast<std::uint32_t>(ceilDiv(desc.n, tile_n));
     state.grid_y               = static_cast<std::uint32_t>(ceilDiv(desc.m, tile_m));
-    state.block                = kThreads;
-    state.smem_bytes           = state.variant == kVariantGeneric ? 0 : kSmemBytes;
+    state.block                = small ? kSmallThreads : kThreads;
+    state.smem_bytes           = (state.variant == kVariantGeneric || small) ? 0 : kSmemBytes;
 
     state.splits      = 1;
     state.k_per_split = static_cast<std::uint32_t>(ceilDiv(desc.k == 0 ? 1 : desc.k, tile_k) * tile_k);
@@ -446,7 +546,7 @@ int configureSimt(LaunchState& state, bool split_k, char* message, std::size_t c
     state.grid_z          = state.splits;
     state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
 
-    if (state.variant != kVariantGeneric) {
+    if (state.variant != kVariantGeneric && state.variant != kVariantSmall) {
         const std::uint64_t a_pitch =
             static_cast<std::uint64_t>((state.variant & kVariantMaskA) == kVariantTmaAk ? desc.a_row_stride : desc.a_col_stride) * sizeof(float);
         const bool a_encoded =
@@ -490,7 +590,7 @@ void planSimtGenericSplitK(LaunchState& state, std::uint32_t splits) {
 cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t stream) {
     const SimtParams out = makeOutputParams(state, workspace);
     const dim3 grid(state.grid_x, state.grid_y, state.grid_z);
-    if (state.variant == kVariantGeneric) {
+    if (state.variant == kVariantGeneric || state.variant == kVariantSmall) {
         GenericParams g{};
         g.a            = state.desc.a;
         g.b            = state.desc.b;
@@ -499,7 +599,11 @@ cudaError_t launchSimt(const LaunchState& state, void* workspace, cudaStream_t s
         g.b_row_stride = state.desc.b_row_stride;
         g.b_col_stride = state.desc.b_col_stride;
         g.out          = out;
-        simtGemmGeneric<<<grid, state.block, 0, stream>>>(g);
+        if (state.variant == kVariantSmall) {
+            simtGemmSmall<<<grid, state.block, 0, stream>>>(g);
+        } else {
+            simtGemmGeneric<<<grid, state.block, 0, stream>>>(g);
+        }
     } else {
         const bool a_k = (state.variant & kVariantMaskA) == kVariantTmaAk;
         const bool b_k = (state.variant & kVariantFlagBk) != 0;

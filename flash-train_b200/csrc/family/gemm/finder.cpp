@@ -26,6 +26,8 @@ std::uint64_t ceilDiv(std::uint64_t x, std::uint64_t y) { return (x + y - 1) / y
 //     out the waves; the unsplit kernels follow for callers without workspace.
 //     With a medium K (512 ... 2047) the split pays only while the tiles fill
 //     under a quarter of a wave (two launches; the partial sums stay small).
+//   * small outputs with a short K: exact-FP32 SIMT on 32x32 tiles ahead of the
+//     tensor kernel (see below).
 //   * everything else: exact-FP32 SIMT, split along K when its 128x128 tiles
 //     leave most SMs idle and K >= 512.
 // Every list ends with "Fp32Gemm", which needs no workspace and accepts every
@@ -80,6 +82,18 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     }
 
     const std::uint64_t simt_tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 128);
+    // Small outputs with a short K (64^3 ... 256^3, 384 x 256 x 320): the exact kernel runs them on 32 x 32
+    // tiles -- many CTAs, a short K loop each -- in about 6 to 10 us of device time, where the tensor
+    // kernel's pipeline set-up and cluster exchange cost over 20 (256^3: 10.3 against 22.2 us). The
+    // condition mirrors the one under which the platform picks that tiling; up to about 48 M
+    // multiply-adds the exact kernel stays ahead (at 512^3 the two are level).
+    const std::uint64_t tiles64 = ceilDiv(shape.m, 64) * ceilDiv(shape.n, 64);
+    const std::uint64_t tiles32 = ceilDiv(shape.m, 32) * ceilDiv(shape.n, 32);
+    if (shape.m >= 33 && (shape.k <= 512 || (shape.k <= 1024 && tiles32 >= 32)) && tiles64 * 4 <= sm_count &&
+        tiles32 <= 2 * sm_count && shape.m * shape.n * shape.k <= (48ULL << 20)) {
+        if (shape.n >= 128 && shape.k >= 256) { return {simt, tensor}; }
+        return {simt};
+    }
     if (shape.m >= 33 && shape.n >= 128 && shape.k >= 256) {
         const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 192);
         const std::uint64_t waves = ceilDiv(tiles, sm_count);

@@ -260,6 +260,10 @@ TEST(finder_regime_map) {
     CHECK(first(48, 65536, 512).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(64, 256, 4096).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(65, 256, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
+    // Small outputs with a short K: the exact kernel's 32 x 32 tiling comes first, the tensor kernel behind it.
+    CHECK(first(256, 256, 256) == (Names{"Fp32Gemm", "Fp32Gemm3xTf32"}));
+    CHECK(first(384, 256, 320) == (Names{"Fp32Gemm", "Fp32Gemm3xTf32"}));
+    CHECK(first(512, 512, 512).front() != "Fp32Gemm");
     CHECK(first(17, 1024, 1024).front() == "Fp32GemmSkinny");
     CHECK(first(17, 2048, 512).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(64, 1024, 1024).front() == "Fp32Gemm3xTf32FewRows");
