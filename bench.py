@@ -29,7 +29,8 @@ copy-out of successive bands overlap; all of it is inside the timed region.
 With N > 1 every rank uploads 1/N of B's rows and the ranks all-gather the rest over NVLink.
 
 Riding along in the default line (each a few launches, after the timed region):
-  `configs`      the other benchmark configurations on this GPU, timed the way the reference's
+  `configs`      the other benchmark configurations on this GPU (and one grouped GEMM of eight ragged
+                 groups: one persistent tensor-core launch against one launch per group), timed the way the reference's
                  benchmark suite times (warm-up 10, about 200 ms of single event-timed calls clamped to
                  [10, 200], median plus mean / min / p10 / p90; benchmarks/ftrain_bench/timing.py:21-44
                  there): the 128x64x96 default, 4096^3 with addend on the exact-FP32 and on the 3xTF32
@@ -354,18 +355,7 @@ def run_reference_arm(options) -> int:
 
 def plan_reuse_native(device_index: int) -> dict | None:
     """The C++ harness (no binding cost): one Plan for m=n=k=1024, 1000 executes."""
-    binary = REPO / "flash-train_b200" / "python" / "flash_train" / "bin" / "plan_reuse_bench"
-    if not binary.exists():
-        return None
-    environment = dict(os.environ)
-    visible = environment.get("CUDA_VISIBLE_DEVICES")
-    devices = visible.split(",") if visible else None
-    environment["CUDA_VISIBLE_DEVICES"] = devices[device_index] if devices else str(device_index)
-    result = subprocess.run([str(binary), "1024", "1024", "1024", "1000", "0"], capture_output=True, text=True,
-                            env=environment, timeout=300)
-    if result.returncode != 0:
-        return {"error": result.stderr.strip()[-300:]}
-    return json.loads(result.stdout.strip().splitlines()[-1])
+    return native_harness(device_index, 1024, 1024, 1024, 1000)
 
 
 def plan_reuse_overhead(capi, torch, device) -> dict:
@@ -496,6 +486,48 @@ def config_records(torch, capi, device, peaks, ffma_tflops) -> dict:
                 "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4),
                 "peak_source": f"{peaks['source']} hbm_gbs (copy); fraction from the back-to-back time"}
     del copies
+    # --- grouped GEMM (GroupedABCDGemm): eight "experts" with ragged token counts, one empty, x @ W_g per group
+    from flash_train.capi import GroupedGemmBinding
+
+    counts, hidden, out_features = [1800, 0, 129, 2515, 1024, 64, 2048, 612], 4096, 4096
+    tokens = torch.randn(sum(counts), hidden, device=device)
+    weights = torch.randn(len(counts), hidden, out_features, device=device) / hidden ** 0.5
+    result = torch.empty(sum(counts), out_features, device=device)
+    starts = [sum(counts[:g]) for g in range(len(counts))]
+    groups = len(counts)
+    rows_of = lambda width: {"row_strides": [width] * groups, "col_strides": [1] * groups}  # noqa: E731
+    grouped_plan = GroupedGemmBinding().make_plan(
+        {"address": tokens.data_ptr(), "rows": counts, "cols": [hidden] * groups, "offsets": [s * hidden for s in starts], **rows_of(hidden)},
+        {"address": weights.data_ptr(), "rows": [hidden] * groups, "cols": [out_features] * groups,
+         "offsets": [g * hidden * out_features for g in range(groups)], **rows_of(out_features)},
+        {"address": 0, "rows": counts, "cols": [out_features] * groups, "offsets": [s * out_features for s in starts], **rows_of(out_features)},
+        {"address": result.data_ptr(), "rows": counts, "cols": [out_features] * groups, "offsets": [s * out_features for s in starts],
+         **rows_of(out_features)}, 1.0, 0.0)
+    grouped_flops = 2.0 * sum(counts) * hidden * out_features
+    stream = torch.cuda.current_stream().cuda_stream
+    grouped = {"groups": groups, "rows_per_group": counts, "k": hidden, "n": out_features, "plan": grouped_plan.primitive_names()}
+    for index, name in enumerate(grouped_plan.primitive_names()):
+        size = grouped_plan.workspace_bytes(index)
+        workspace = torch.empty(max(size, 1), dtype=torch.uint8, device=device)
+        call = lambda: grouped_plan.execute(index, workspace.data_ptr() if size else 0, size, stream)  # noqa: E731
+        stats = measure_calls(torch, call)
+        tflops = grouped_flops / (stats["median_us"] * 1e-6) / 1e12
+        peak, bound = (burst_tensor, "tensor") if "3xTf32" in name else (ffma_tflops, "fp32")
+        grouped[name] = {**stats, "tflops": round(tflops, 2), "bound": bound, "frac": round(tflops / peak, 4) if peak else None,
+                         "workspace_bytes": size}
+    # The same products as separate Plans of the plain Gemm, one launch each, for comparison.
+    singles = [PlanRunner(torch, tokens[s:s + count], weights[g], None, result[s:s + count])
+               for g, (s, count) in enumerate(zip(starts, counts)) if count]
+
+    def one_by_one():
+        for runner in singles:
+            runner.run()
+
+    stats = measure_calls(torch, one_by_one)
+    grouped["one_plain_gemm_per_group"] = {**stats, "tflops": round(grouped_flops / (stats["median_us"] * 1e-6) / 1e12, 2),
+                                           "primitives": sorted({runner.name for runner in singles})}
+    records["grouped_gemm_8_ragged_groups_k4096_n4096"] = grouped
+    del tokens, weights, result, singles
     # --- 1024^3, the Plan-reuse shape: device time of the selected kernel
     a, b = torch.randn(1024, 1024, device=device), torch.randn(1024, 1024, device=device)
     d = torch.empty(1024, 1024, device=device)
@@ -509,33 +541,46 @@ def config_records(torch, capi, device, peaks, ffma_tflops) -> dict:
     return records
 
 
+def native_harness(device_index: int, m: int, k: int, n: int, calls: int) -> dict | None:
+    """The C++ harness (no binding in the way) for one shape: Plan-reuse host time and the tiers' medians."""
+    binary = REPO / "flash-train_b200" / "python" / "flash_train" / "bin" / "plan_reuse_bench"
+    if not binary.exists():
+        return None
+    environment = dict(os.environ)
+    visible = environment.get("CUDA_VISIBLE_DEVICES")
+    devices = visible.split(",") if visible else None
+    environment["CUDA_VISIBLE_DEVICES"] = devices[device_index] if devices else str(device_index)
+    result = subprocess.run([str(binary), str(m), str(k), str(n), str(calls), "0"], capture_output=True, text=True,
+                            env=environment, timeout=300)
+    if result.returncode != 0:
+        return {"error": result.stderr.strip()[-300:]}
+    return json.loads(result.stdout.strip().splitlines()[-1])
+
+
 def tier_records(torch, capi, ft_torch, device) -> dict:
     """The reference's published tiers (its README's L1-L4) at its published shapes, same timing policy,
-    alpha 1, beta 0, no C: L1 the Python call, L2 the one-shot C call, L3 Plan reuse (primitive 0), L4 every
-    primitive of the Plan. `published_us` are the reference's own medians on its own hardware."""
-    from flash_train.capi import null_operand, tensor_operand
-
-    stream = torch.cuda.current_stream().cuda_stream
+    alpha 1, beta 0, no C: L1 the Python call (timed here), L2 the one-shot C call, L3 Plan reuse
+    (primitive 0) and L4 every primitive of the Plan (timed by the C++ harness, as the reference times them
+    from its C harness). `published_us` are the reference's own medians on its own hardware."""
     records = {}
     for size in (64, 128, 256):
         a, b = torch.randn(size, size, device=device), torch.randn(size, size, device=device)
         d = torch.empty(size, size, device=device)
-        runner = PlanRunner(torch, a, b, None, d)
         tiers = {"L1_python": measure_calls(torch, lambda: ft_torch.gemm(a, b))["median_us"],
-                 "L2_one_shot": measure_calls(torch, lambda: capi.gemm_once(tensor_operand(a), tensor_operand(b), null_operand(size, size),
-                                                                            tensor_operand(d), 1.0, 0.0, stream=stream))["median_us"],
-                 "L3_plan_reuse": measure_calls(torch, runner.run)["median_us"],
                  "torch_matmul": measure_calls(torch, lambda: torch.matmul(a, b, out=d))["median_us"]}
-        per_primitive = {}
-        for name in runner.names:
-            per_primitive[name] = measure_calls(torch, PlanRunner(torch, a, b, None, d, primitive=name).run)["median_us"]
+        native = native_harness(device.index or 0, size, size, size, 200)
+        per_primitive = None
+        if native is not None and "tiers" in native:
+            tiers["L2_one_shot"] = native["tiers"]["L2_one_shot"]["median_us"]
+            tiers["L3_plan_reuse"] = native["tiers"]["L3_plan_reuse"]["median_us"]
+            per_primitive = {name: timing["median_us"] for name, timing in native["tiers"]["L4_per_primitive"].items()}
         published = PUBLISHED_TIERS_US[size]
         records[f"{size}x{size}x{size}"] = {
-            "median_us": tiers, "L4_per_primitive_us": per_primitive, "plan": runner.names, "published_us": published,
-            "published_over_ours": {key: round(published[key] / tiers[key], 2) for key in published}}
+            "median_us": tiers, "L4_per_primitive_us": per_primitive, "published_us": published,
+            "published_over_ours": {key: round(published[key] / tiers[key], 2) for key in published if key in tiers}}
     records["note"] = ("published_us: the reference's medians for its kernel on a Hygon BW1102 "
-                       "(benchmarks/results/gemm-fp32-*.json there); other hardware, same timing policy; "
-                       "L2 here goes through the Python ctypes binding")
+                       "(benchmarks/results/gemm-fp32-*.json there); other hardware, same timing policy "
+                       "(every call between its own pair of events, so launch and event overhead are in every figure)")
     return records
 
 

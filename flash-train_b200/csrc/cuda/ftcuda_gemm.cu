@@ -12,7 +12,23 @@ using ftcuda::LaunchState;
 
 static_assert(std::is_trivially_copyable<LaunchState>::value, "a launch must be copyable with the Primitive");
 
+bool stagesOperands(int kernel) {
+    return kernel == FTCUDA_GEMM_TF32X3 || kernel == FTCUDA_GEMM_TF32X3_SPLITK || kernel == FTCUDA_GEMM_TF32X3_ROWS;
+}
+
+const char* supportsAsGiven(int kernel, const FtcudaGemmDesc& desc);
+
+// The tensor-core families take operands TMA cannot describe through a copy in the workspace: their
+// own rules are asked about the problem with those operands replaced by the copies' description.
 const char* supports(int kernel, const FtcudaGemmDesc& desc) {
+    if (!stagesOperands(kernel)) { return supportsAsGiven(kernel, desc); }
+    LaunchState probe{};
+    probe.desc = desc;
+    if (const char* reason = ftcuda::planStaging(kernel, desc, probe)) { return reason; }
+    return supportsAsGiven(kernel, probe.desc);
+}
+
+const char* supportsAsGiven(int kernel, const FtcudaGemmDesc& desc) {
     switch (kernel) {
         case FTCUDA_GEMM_SIMT: return ftcuda::supportsSimt(desc, false);
         case FTCUDA_GEMM_SIMT_SPLITK: return ftcuda::supportsSimt(desc, true);
@@ -42,14 +58,25 @@ extern "C" int ftcuda_gemm_configure(int kernel, const FtcudaGemmDesc* desc, Ftc
     LaunchState& state = *reinterpret_cast<LaunchState*>(launch);
     state.desc         = *desc;
     state.kernel       = kernel;
-    switch (kernel) {
-        case FTCUDA_GEMM_SIMT: return ftcuda::configureSimt(state, false, message, message_capacity);
-        case FTCUDA_GEMM_SIMT_SPLITK: return ftcuda::configureSimt(state, true, message, message_capacity);
-        case FTCUDA_GEMM_TF32X3: return ftcuda::configureTensor(state, false, message, message_capacity);
-        case FTCUDA_GEMM_TF32X3_SPLITK: return ftcuda::configureTensor(state, true, message, message_capacity);
-        case FTCUDA_GEMM_TF32X3_ROWS: return ftcuda::configureTensorRows(state, message, message_capacity);
-        default: return ftcuda::configureSkinny(state, message, message_capacity);
+    if (stagesOperands(kernel)) {
+        // state.desc now describes the copies; the family configures itself for them.
+        if (const char* staging = ftcuda::planStaging(kernel, *desc, state)) { return ftcuda::fail(message, message_capacity, 1, "%s", staging); }
     }
+    int status = 0;
+    switch (kernel) {
+        case FTCUDA_GEMM_SIMT: status = ftcuda::configureSimt(state, false, message, message_capacity); break;
+        case FTCUDA_GEMM_SIMT_SPLITK: status = ftcuda::configureSimt(state, true, message, message_capacity); break;
+        case FTCUDA_GEMM_TF32X3: status = ftcuda::configureTensor(state, false, message, message_capacity); break;
+        case FTCUDA_GEMM_TF32X3_SPLITK: status = ftcuda::configureTensor(state, true, message, message_capacity); break;
+        case FTCUDA_GEMM_TF32X3_ROWS: status = ftcuda::configureTensorRows(state, message, message_capacity); break;
+        default: status = ftcuda::configureSkinny(state, message, message_capacity); break;
+    }
+    if (status == 0 && state.staged != 0) {
+        // The copies take the head of the workspace (plus room to align them), the family's own needs follow.
+        state.stage_bytes += 256;
+        state.workspace_bytes += state.stage_bytes;
+    }
+    return status;
 }
 
 extern "C" uint64_t ftcuda_gemm_workspace_bytes(const FtcudaGemmLaunch* launch) {
@@ -71,6 +98,26 @@ extern "C" int ftcuda_gemm_launch(const FtcudaGemmLaunch* launch, void* workspac
     }
     const cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
     cudaError_t error              = cudaSuccess;
+    if (state.staged != 0) {
+        // Copy the operands TMA cannot fetch into the head of the workspace, point a copy of the launch's
+        // descriptors at them, and hand the rest of the workspace to the kernel family.
+        LaunchState local = state;
+        if (message != nullptr && message_capacity != 0) { message[0] = '\0'; }
+        error = ftcuda::runStaging(local, workspace, cuda_stream, message, message_capacity);
+        if (error != cudaSuccess) {
+            if (message != nullptr && message_capacity != 0 && message[0] != '\0') { return 1; }
+            return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error));
+        }
+        void* const rest = static_cast<unsigned char*>(workspace) + local.stage_bytes;
+        local.workspace_bytes -= local.stage_bytes;
+        if (local.kernel == FTCUDA_GEMM_TF32X3_ROWS) {
+            error = ftcuda::launchTensorRows(local, cuda_stream);
+        } else {
+            error = ftcuda::launchTensor(local, rest, cuda_stream);
+        }
+        if (error != cudaSuccess) { return ftcuda::fail(message, message_capacity, 1, "%s", cudaGetErrorString(error)); }
+        return 0;
+    }
     switch (state.kernel) {
         case FTCUDA_GEMM_SIMT:
         case FTCUDA_GEMM_SIMT_SPLITK: error = ftcuda::launchSimt(state, workspace, cuda_stream); break;
@@ -94,6 +141,9 @@ extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* 
     }
     if ((state.variant & ftcuda::kVariantFlagPair) != 0) {
         return ftcuda::fail(message, message_capacity, 1, "the CTA-pair form has no scatter epilogue");
+    }
+    if (state.staged != 0) {
+        return ftcuda::fail(message, message_capacity, 1, "scatter launches take operands TMA can fetch as they are (no staging)");
     }
     if (owners < 1 || owners > 8) { return ftcuda::fail(message, message_capacity, 1, "1 to 8 owners, got %d", owners); }
     if (rows_per_owner == 0 || rows_per_owner >= (1ULL << 31) || rows_per_owner * static_cast<uint64_t>(owners) < state.desc.m) {

@@ -25,6 +25,16 @@ enum Variant : int {
     kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
     kVariantFlagPair = 32,  // tensor kernel: CTA pairs on 256-row tiles
     kVariantFlagCluster = 64,  // tensor kernel: the K slices of a tile form a thread-block cluster (one launch)
+    kVariantFlagEarlyStart = 128,  // ... launched with programmatic stream serialization (set-up overlaps the predecessor's tail)
+};
+
+// One operand copied into the workspace before the launch (see LaunchState::staged).
+struct StagedOperand {
+    const float* source;
+    std::int64_t row_stride, col_stride;  // of the source, in elements
+    std::uint64_t rows, cols;
+    std::uint64_t pitch;                   // elements between rows of the copy, a multiple of four
+    std::uint64_t offset;                  // byte offset of the copy in the workspace, a multiple of 256
 };
 
 // What ftcuda_gemm_configure stores inside an FtcudaGemmLaunch.
@@ -45,6 +55,13 @@ struct LaunchState {
     std::uint64_t workspace_bytes;
     int* device_status;            // mapped host word the kernels report a timed-out wait in
     volatile int* host_status;
+    // Operand staging (tensor-core families): an A or B whose layout TMA cannot describe (a transposed
+    // view with an odd pitch, a misaligned base, two non-unit strides) is first copied, by a small
+    // kernel, into the head of the workspace as a dense row-major matrix with a 16-byte row pitch; the
+    // TMA descriptors were made for that copy and get its address in front of every launch.
+    std::uint32_t staged;          // bit 0: A is staged, bit 1: B
+    StagedOperand stage[2];
+    std::uint64_t stage_bytes;     // bytes at the head of the workspace taken by the copies
 };
 static_assert(sizeof(LaunchState) <= sizeof(FtcudaGemmLaunch), "launch blob too small");
 static_assert(alignof(FtcudaGemmLaunch) >= 64, "launch blob must be 64-byte aligned");
@@ -85,6 +102,15 @@ void countLaunches(std::uint64_t launches);
 // row pitch a positive multiple of 16 bytes that fits 2^40, extents < 2^32.
 bool tmaEligible(const void* base, std::int64_t contiguous_stride, std::int64_t other_stride,
                  std::uint64_t contiguous_extent, std::uint64_t other_extent);
+
+// ---- operand staging (gemm_stage.cu) ----
+// Decides which operands of `desc` kernel family `kernel` cannot fetch by TMA as they are, records
+// them in `state` (staged, stage[], stage_bytes) and rewrites state.desc to describe the copies
+// (dense row-major, placeholder addresses of the right alignment). Returns a reason when an operand
+// can be neither fetched nor staged, else nullptr. Pure host arithmetic.
+const char* planStaging(int kernel, const FtcudaGemmDesc& desc, LaunchState& state);
+// Enqueues the copies into `workspace` and points the launch's TMA descriptors at them.
+cudaError_t runStaging(LaunchState& local, void* workspace, cudaStream_t stream, char* message, std::size_t capacity);
 
 // ---- kernel families ----
 // supports*: nullptr when the family can run the problem, else the reason.

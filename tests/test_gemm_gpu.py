@@ -281,6 +281,11 @@ def test_config3_tail_sweep_contiguous_and_transposed(capi, gpu, oracle, m):
         assert gpu.make_plan(a_view, b, None, d).primitive_names() == names
     if m <= 17:
         assert gpu.make_plan(a, b, None, d).primitive_name(0) == ("Fp32GemmSkinny" if m == 1 else "Fp32Gemm3xTf32FewRows")
+    if m >= 17:
+        # The transposed view of a k x m buffer with an odd m has a pitch TMA cannot take; the tensor-core
+        # Primitives still come first: they stage A in the workspace (and ask for one).
+        staged = gpu.make_plan(buffer.t(), b, None, d)
+        assert staged.primitive_name(0).startswith("Fp32Gemm3xTf32") and staged.workspace_bytes(0) >= m * k * 4
     # The one-shot call takes no workspace here and must still succeed.
     once = torch.empty(m, n, device="cuda")
     capi.gemm_once(gpu.operand(a), gpu.operand(b), capi.null_operand(m, n), gpu.operand(once), 1.0, 0.0,
@@ -629,11 +634,16 @@ def test_tensor_few_rows_kernel(capi, gpu, oracle, m):
         d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, a, bt, c, 1.5, -0.25)
         assert d is not None, reason
         check_against_float64(oracle, d, a, bt.contiguous(), c, 1.5, -0.25, f"tensor few rows, B along K, m={m} k={k} n={n}")
-    # Declined: too many rows, A stored by columns, short K.
+    # Declined: too many rows, short K.
     wide = torch.randn(65, 512, device="cuda")
     assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, wide, torch.randn(512, 256, device="cuda"), None, 1.0, 0.0)[0] is None
-    assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, torch.randn(512, 8, device="cuda").t(),
-                         torch.randn(512, 256, device="cuda"), None, 1.0, 0.0)[0] is None
+    # A stored by columns (the transposed view of a k x m buffer, whatever its pitch) is copied into the
+    # workspace as a row-major matrix first: accepted, with a workspace.
+    a_t = torch.randn(512, m, device="cuda").t()
+    b = torch.randn(512, 256, device="cuda")
+    d, reason = platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, a_t, b, None, 1.0, 0.0)
+    assert d is not None, reason
+    check_against_float64(oracle, d, a_t.contiguous(), b, None, 1.0, 0.0, f"tensor few rows, A staged, m={m}")
     assert platform_gemm(capi, gpu, capi.KERNEL_TF32X3_ROWS, torch.randn(8, 64, device="cuda"), torch.randn(64, 256, device="cuda"),
                          None, 1.0, 0.0)[0] is None
 
@@ -720,3 +730,41 @@ def test_a_wait_that_runs_out_is_reported_once_and_the_device_stays_usable(capi,
     gpu.run_plan(plan)
     torch.cuda.synchronize()
     assert torch.allclose(d, a @ b, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("kernel", [1, 2, 5])
+def test_operands_tma_cannot_fetch_are_staged_in_the_workspace(capi, gpu, oracle, kernel):
+    """A and/or B with layouts no TMA descriptor describes -- transposed views with odd pitches, a base in
+    the middle of a row, two non-unit strides -- run on the tensor-core families through a copy at the head
+    of the workspace; with split-K the partial sums follow the copies in the same workspace."""
+    import os
+
+    if os.environ.get("FT_SKIP_TENSOR"):
+        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
+    torch.manual_seed(83)
+    rows_kernel = kernel == capi.KERNEL_TF32X3_ROWS
+    m, k, n = (33, 2048, 513) if rows_kernel else (255, 2304, 517)
+    cases = {
+        "A transposed, odd pitch": (torch.randn(k, m, device="cuda").t(), torch.randn(k, n + 3, device="cuda")[:, :n + 3][:, :n]),
+        "A off a 16-byte boundary": (torch.randn(m, k + 5, device="cuda")[:, 1:k + 1], torch.randn(k, n + 3, device="cuda")[:, :n]),
+        "A every other column, B transposed with odd pitch": (torch.randn(m, 2 * k, device="cuda")[:, ::2],
+                                                             torch.randn(n, k + 1, device="cuda")[:, :k].t()),
+        "only B staged": (torch.randn(m, k, device="cuda"), torch.randn(k, n, device="cuda")),
+    }
+    c = torch.randn(m, n, device="cuda")
+    for label, (a, b) in cases.items():
+        d = torch.full((m, n), float("nan"), device="cuda")
+        desc = capi.make_desc(gpu.operand(a), gpu.operand(b), gpu.operand(c), gpu.operand(d), 1.25, -0.5, torch.cuda.current_device())
+        reason = capi.platform_supports(kernel, desc)
+        assert reason is None, f"{label}: {reason}"
+        launch = capi.PlatformGemm(kernel, desc)
+        assert launch.workspace_bytes > 0, label
+        # An oddly aligned workspace must do: the copies are aligned inside it.
+        workspace = torch.empty(launch.workspace_bytes + 8, dtype=torch.uint8, device="cuda")
+        for _ in range(2):
+            d.fill_(float("nan"))
+            launch.run(workspace.data_ptr() + 4, launch.workspace_bytes, gpu.current_stream())
+            torch.cuda.synchronize()
+            check_against_float64(oracle, d, a.contiguous(), b.contiguous(), c, 1.25, -0.5, f"{capi.KERNEL_NAMES[kernel]}, {label}")
+        with pytest.raises(capi.FTrainError, match="workspace"):
+            launch.run(0, 0, gpu.current_stream())
