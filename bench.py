@@ -485,6 +485,19 @@ def config_records(torch, capi, device, peaks, ffma_tflops) -> dict:
                 "primitive": runners[0].name, **stats, "back_to_back_us": round(chained, 3), "bound": "hbm",
                 "gbs": round(gbs, 1), "frac": round(gbs / peaks["hbm_gbs"], 4),
                 "peak_source": f"{peaks['source']} hbm_gbs (copy); fraction from the back-to-back time"}
+    # ... and the compute-bound members of the same sweep, m = 255 and 4097 (one B is enough: 137 GFLOP and more
+    #     per call). The transposed view of a k x m buffer with an odd m has a pitch TMA cannot take: the
+    #     tensor-core Primitive stages A in its workspace first (one more small launch).
+    for m in (255, 4097):
+        plain = torch.rand(m, 4096, device=device, generator=generator) * 2 - 1
+        for label, a in (("contiguous", plain), ("transposed_view", plain.t().contiguous().t())):
+            d = torch.empty(m, 4096, device=device)
+            runner = PlanRunner(torch, a, copies[0], None, d)
+            stats = measure_calls(torch, runner.run)
+            tflops = 2.0 * m * 4096 * 4096 / (stats["median_us"] * 1e-6) / 1e12
+            records[f"config3_{m}x4096x4096_{label}"] = {
+                "primitive": runner.name, "workspace_bytes": runner.size, **stats, "bound": "tensor", "tflops": round(tflops, 2),
+                "frac": round(tflops / burst_tensor, 4), "peak_source": f"{peaks['source']} bf16_tflops / 6"}
     del copies
     # --- grouped GEMM (GroupedABCDGemm): eight "experts" with ragged token counts, one empty, x @ W_g per group
     from flash_train.capi import GroupedGemmBinding
