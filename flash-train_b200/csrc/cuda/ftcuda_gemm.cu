@@ -139,9 +139,6 @@ extern "C" int ftcuda_gemm_launch_scatter(const FtcudaGemmLaunch* launch, void* 
     if (state.kernel != FTCUDA_GEMM_TF32X3 && state.kernel != FTCUDA_GEMM_TF32X3_SPLITK) {
         return ftcuda::fail(message, message_capacity, 1, "scatter launches exist for the tensor-core kernels only");
     }
-    if ((state.variant & ftcuda::kVariantFlagPair) != 0) {
-        return ftcuda::fail(message, message_capacity, 1, "the CTA-pair form has no scatter epilogue");
-    }
     if (state.staged != 0) {
         return ftcuda::fail(message, message_capacity, 1, "scatter launches take operands TMA can fetch as they are (no staging)");
     }

@@ -23,7 +23,6 @@ enum Variant : int {
     kVariantSmall    = 3,  // SIMT only: 32 x 32 tiles with register prefetch, for outputs too small to fill the SMs otherwise
     kVariantMaskA    = 15,
     kVariantFlagBk   = 16,  // tensor kernel: B contiguous along K (transposed view of an N x K buffer)
-    kVariantFlagPair = 32,  // tensor kernel: CTA pairs on 256-row tiles
     kVariantFlagCluster = 64,  // tensor kernel: the K slices of a tile form a thread-block cluster (one launch)
     kVariantFlagEarlyStart = 128,  // ... launched with programmatic stream serialization (set-up overlaps the predecessor's tail)
 };
@@ -120,12 +119,6 @@ cudaError_t runStaging(LaunchState& local, void* workspace, cudaStream_t stream,
 namespace tf32x3 {
 struct TensorParams;
 }
-// CTA-pair form of the tensor kernel (gemm_tf32x3_pair.cu), used by configureTensor / launchTensor.
-bool tensorPairEnabled();  // FTCUDA_TF32_PAIR=1 switches it on
-int configureTensorPair(LaunchState& state, char* message, std::size_t capacity);
-cudaError_t launchTensorPair(const LaunchState& state, const tf32x3::TensorParams& p, std::uint32_t items,
-                             cudaStream_t stream);
-
 // 3xTF32 for few rows of A with the operands' roles swapped (gemm_tf32x3_rows.cu).
 const char* supportsTensorRows(const FtcudaGemmDesc& desc);
 int configureTensorRows(LaunchState& state, char* message, std::size_t capacity);

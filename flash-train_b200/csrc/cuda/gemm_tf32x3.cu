@@ -649,21 +649,6 @@ int configureTensor(LaunchState& state, bool split_k, char* message, std::size_t
         state.k_per_split = static_cast<std::uint32_t>(ceilDiv(ceilDiv(desc.k, wanted), kTileK) * kTileK);
         state.splits      = static_cast<std::uint32_t>(ceilDiv(desc.k, state.k_per_split));
     }
-    // CTA pairs (gemm_tf32x3_pair.cu) take 256-row tiles, two SMs per tile. Opt-in.
-    const std::uint64_t pair_tiles = ceilDiv(desc.m, 2 * kTileM) * ceilDiv(desc.n, kTileN);
-    const std::uint64_t pairs      = static_cast<std::uint64_t>(sms / 2);
-    const bool use_pairs = tensorPairEnabled() && desc.m > kTileM && pairs >= 1 &&
-                           ceilDiv(pair_tiles * state.splits, pairs) * 9 <= ceilDiv(tiles * state.splits, static_cast<std::uint64_t>(sms)) * 10;
-    if (use_pairs) {
-        state.variant |= kVariantFlagPair;
-        const std::uint64_t pair_items = pair_tiles * state.splits;
-        state.grid_x          = static_cast<std::uint32_t>(2 * (pair_items < pairs ? pair_items : pairs));
-        state.grid_y          = 1;
-        state.grid_z          = 1;
-        state.chunk_k_blocks  = chunkKBlocks(desc.k);
-        state.workspace_bytes = state.splits > 1 ? static_cast<std::uint64_t>(state.splits) * desc.m * desc.n * sizeof(float) : 0;
-        return configureTensorPair(state, message, capacity);
-    }
     // Few tiles and a K worth cutting, in the single-launch family: the K slices of a tile become a
     // thread-block cluster that meets through distributed shared memory -- no workspace, no second
     // kernel. The twelve 16-column pieces of a tile are dealt out to the CTAs, hence 2, 3, 4 or 6.
@@ -783,15 +768,9 @@ cudaError_t launchTensor(const LaunchState& state, void* workspace, cudaStream_t
         countLaunches(1);
         return error;
     }
-    if ((state.variant & kVariantFlagPair) != 0) {
-        p.tiles_m      = static_cast<std::uint32_t>(ceilDiv(desc.m, 2 * kTileM));
-        p.band_m_tiles = p.band_m_tiles > 1 ? p.band_m_tiles / 2 : 1;
-        error          = launchTensorPair(state, p, p.tiles_m * p.tiles_n * p.splits, stream);
-    } else {
-        const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
-        tensorGemm3xTf32<false><<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
-        error = cudaGetLastError();
-    }
+    const std::uint32_t items = p.tiles_m * p.tiles_n * p.splits;
+    tensorGemm3xTf32<false><<<state.grid_x, state.block, state.smem_bytes, stream>>>(state.map_a, state.map_b, p, items);
+    error = cudaGetLastError();
     std::uint64_t launches = 1;
     if (error == cudaSuccess && state.splits > 1) {
         error = launchSplitKReduce(desc, static_cast<const float*>(workspace), state.splits, stream);

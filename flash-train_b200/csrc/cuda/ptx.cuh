@@ -243,11 +243,7 @@ __device__ __forceinline__ void umaCommit(std::uint64_t* barrier) {
                  : "memory");
 }
 
-// ---------------------------------------------------------------- CTA pairs (cta_group::2)
-// Two CTAs of a cluster (ranks 2i and 2i+1) whose tensor cores work on one
-// 256-row tile: the even CTA issues the MMAs, each CTA holds its 128 rows of A
-// and D in its own tensor memory and half of the B tile in its own shared
-// memory, at the same addresses in both.
+// ---------------------------------------------------------------- thread-block clusters
 
 __device__ __forceinline__ std::uint32_t clusterCtaRank() {
     std::uint32_t rank;
@@ -256,85 +252,6 @@ __device__ __forceinline__ std::uint32_t clusterCtaRank() {
 }
 __device__ __forceinline__ void clusterBarrierArrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void clusterBarrierWait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-// Whole-warp calls, made by the warp with the same index in BOTH CTAs of the
-// pair, with the same shared-memory offset for the result.
-__device__ __forceinline__ void tmemAllocatePair(std::uint32_t* result_in_smem, std::uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddress(result_in_smem)),
-                 "r"(columns)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmemFreePair(std::uint32_t base, std::uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
-}
-
-// Arrives (release, cluster scope) on the barrier at the same shared-memory
-// offset as `barrier` in the CTA with rank `target_rank` of this cluster.
-__device__ __forceinline__ void mbarrierArriveInCta(std::uint64_t* barrier, std::uint32_t target_rank) {
-    asm volatile(
-        "{\n\t"
-        ".reg .b32 remote;\n\t"
-        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
-        "}" ::"r"(smemAddress(barrier)),
-        "r"(target_rank)
-        : "memory");
-}
-
-// mbarrierWait for a barrier that CTAs of the whole cluster arrive on
-// (acquire at cluster scope).
-__device__ __forceinline__ bool mbarrierTryWaitCluster(std::uint64_t* barrier, std::uint32_t parity) {
-    std::uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(smemAddress(barrier)), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbarrierWaitCluster(std::uint64_t* barrier, std::uint32_t parity,
-                                                    const volatile int* abort_flag) {
-    if (mbarrierTryWaitCluster(barrier, parity)) { return true; }
-    const unsigned long long start = globalTimerNs();
-    std::uint32_t spins            = 0;
-    while (true) {
-        if (mbarrierTryWaitCluster(barrier, parity)) { return true; }
-        if ((++spins & 0xFF) == 0) {
-            if (*abort_flag != 0) { return false; }
-            if (globalTimerNs() - start > kWaitBudgetNs) { return false; }
-        }
-    }
-}
-
-// D[tmem of both CTAs] (+)= A[tmem of both CTAs] * B[shared memory of both
-// CTAs], M = 256 over the pair; issued by ONE thread of the even CTA.
-__device__ __forceinline__ void umaTf32TmemAPair(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_descriptor,
-                                                 std::uint32_t instruction, std::uint32_t accumulate) {
-    const std::uint32_t zero = 0;  // no output lane is masked
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t"
-        "}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_descriptor), "r"(instruction), "r"(accumulate), "r"(zero)
-        : "memory");
-}
-
-// Arrives once on the barrier at this shared-memory offset in every CTA of
-// `cta_mask` when every MMA this thread issued so far has finished.
-__device__ __forceinline__ void umaCommitPair(std::uint64_t* barrier, std::uint16_t cta_mask) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
-            smemAddress(barrier)),
-        "h"(cta_mask)
-        : "memory");
-}
 
 // Whole-warp load of 32 lanes x 32 consecutive 32-bit columns: thread t of the
 // warp receives lane (lane_base + t), columns [column, column + 32). The wait

@@ -1,4 +1,4 @@
-// Pieces shared by the single-CTA and the CTA-pair 3xTF32 tensor-core kernels:
+// Pieces shared by the 3xTF32 tensor-core kernels:
 // kernel parameters, the walk over output tiles, the TF32 split and the
 // epilogue's row-segment writer.
 #pragma once
@@ -77,7 +77,7 @@ struct WorkItem {
     std::uint32_t k_begin, k_blocks;
 };
 
-// `tile_rows`: rows of A per work item (128 for one CTA, 256 for a CTA pair).
+// `tile_rows`: rows of A per work item.
 template<bool kClustered = false>
 __device__ __forceinline__ WorkItem decodeItem(const TensorParams& p, std::uint32_t item, std::uint32_t tile_rows) {
     const std::uint32_t tiles = p.tiles_m * p.tiles_n;

@@ -432,34 +432,6 @@ def test_training_layouts_select_a_tensor_kernel(capi, gpu, oracle):
         check_against_float64(oracle, d, a.contiguous(), b.contiguous(), None, 1.0, 0.0, f"{label} via {names[0]}")
 
 
-@pytest.mark.parametrize("kernel", [1, 2])
-def test_cta_pair_form_of_the_tensor_kernel(capi, gpu, oracle, kernel, monkeypatch):
-    """FTCUDA_TF32_PAIR=1 (read when a launch is configured) selects the cta_group::2 form of the
-    tensor kernel: 256-row tiles over two SMs. Same results as the single-CTA form."""
-    import os
-
-    if os.environ.get("FT_SKIP_TENSOR"):
-        pytest.skip("tensor-core kernels switched off by FT_SKIP_TENSOR")
-    torch.manual_seed(43)
-    # The comparison is bit for bit, so the single-CTA form must not cut K over a cluster here.
-    monkeypatch.setenv("FTCUDA_TF32_CLUSTER_SPLIT", "0")
-    for m, k, n, a_t, b_t in ((384, 320, 400, False, False), (256, 2304, 384, False, False), (700, 200, 4128, True, False),
-                              (1024, 512, 768, False, True), (130, 96, 200, True, True)):
-        a = torch.randn(k, m, device="cuda").t() if a_t else torch.randn(m, k, device="cuda")
-        b = torch.randn(n, k, device="cuda").t() if b_t else torch.randn(k, n, device="cuda")
-        c = torch.randn(m, n, device="cuda")
-        monkeypatch.setenv("FTCUDA_TF32_PAIR", "1")
-        paired, reason = platform_gemm(capi, gpu, kernel, a, b, c, 1.5, -0.75)
-        monkeypatch.delenv("FTCUDA_TF32_PAIR")
-        if paired is None:
-            pytest.skip(f"{capi.KERNEL_NAMES[kernel]} declines: {reason}")
-        single, _ = platform_gemm(capi, gpu, kernel, a, b, c, 1.5, -0.75)
-        check_against_float64(oracle, paired, a.contiguous(), b.contiguous(), c, 1.5, -0.75,
-                              f"pair form {capi.KERNEL_NAMES[kernel]} {m}x{k}x{n}")
-        # Both forms split and sum in the same order within a tile row: identical bits.
-        assert torch.equal(paired, single), f"pair and single forms differ for {m}x{k}x{n}"
-
-
 @pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16, 17, 24, 32])
 def test_few_rows_kernel_with_b_contiguous_along_k(capi, gpu, oracle, m):
     """x @ W^T for few rows of x: B is the transposed view of an n x k weight matrix (dims (k, n),
