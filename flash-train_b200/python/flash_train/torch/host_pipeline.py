@@ -80,8 +80,27 @@ class HostGemm:
             self._copy_in = torch.cuda.Stream(self.device)
             self._copy_out = torch.cuda.Stream(self.device)
 
+    def join(self) -> None:
+        """Makes the caller's current stream wait for the copy-outs of earlier calls (what a call does by itself
+        unless it was made with overlap_calls=True). Does not block the host."""
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream(self.device).wait_stream(self._copy_out)
+
+    def synchronize(self) -> None:
+        """Blocks until every copy and kernel of earlier calls has finished (all three streams)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream(self.device).synchronize()
+            self._copy_in.synchronize()
+            self._copy_out.synchronize()
+
     def __call__(self, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0,
-                 beta: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 beta: float = 0.0, out: Optional[torch.Tensor] = None, overlap_calls: bool = False) -> torch.Tensor:
+        """overlap_calls=False: when the call returns, the caller's current stream waits for the last copy-out,
+        so one synchronize on it is enough before reading `out`. overlap_calls=True: consecutive calls pipeline
+        -- the next call's copy-in starts as soon as this call's kernels have read the device buffers, while
+        this call's results are still leaving --; the caller's stream does NOT wait for the copy-out then:
+        call synchronize() (or synchronise the device) before reading `out`, and give calls whose results are
+        still in flight different `out` buffers or accept that they are written in call order."""
         _check_host_matrix(a, "a")
         _check_host_matrix(b, "b")
         if tuple(a.shape) != (self.m, self.k) or tuple(b.shape) != (self.k, self.n):
@@ -104,9 +123,11 @@ class HostGemm:
         with torch.cuda.device(self.device):
             compute = torch.cuda.current_stream(self.device)
             copy_in, copy_out = self._copy_in, self._copy_out
-            # Buffers of an earlier call (or whatever the caller queued) come first.
+            # Buffers of an earlier call (or whatever the caller queued) come first. The device buffers are
+            # read by kernels on the compute stream only; the products leave through blocks of their own.
             copy_in.wait_stream(compute)
-            copy_in.wait_stream(copy_out)
+            if not overlap_calls:
+                copy_in.wait_stream(copy_out)
             with torch.cuda.stream(copy_in):
                 if self._group is None:
                     self._b.copy_(b, non_blocking=True)
@@ -144,7 +165,8 @@ class HostGemm:
                     # copy-out stream still reads the block.
                     product.record_stream(copy_out)
             # The caller's stream sees the finished result: one synchronize on it is enough.
-            compute.wait_stream(copy_out)
+            if not overlap_calls:
+                compute.wait_stream(copy_out)
         return out
 
 

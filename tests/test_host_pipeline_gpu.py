@@ -55,6 +55,28 @@ def test_host_gemm_matches_float64(binding, oracle, m, n, k, band_rows, with_c):
         check(oracle, out, a, b, c, alpha, beta, f"{m}x{n}x{k} bands of {band_rows}, call {call}")
 
 
+def test_overlapping_calls_write_their_results_in_call_order(binding, oracle):
+    """overlap_calls=True: the next call's copy-in runs while the previous call's result is still leaving; every
+    call's result must still be complete and right after synchronize()."""
+    generator = torch.Generator().manual_seed(5)
+    m, n, k = 1024, 640, 512
+    b = torch.randn(k, n, generator=generator).pin_memory()
+    inputs = [torch.randn(m, k, generator=generator).pin_memory() for _ in range(4)]
+    outputs = [torch.full((m, n), float("nan")).pin_memory() for _ in range(4)]
+    pipeline = binding.HostGemm(m, n, k, band_rows=128)
+    for a, out in zip(inputs, outputs):
+        pipeline(a, b, out=out, overlap_calls=True)
+    pipeline.synchronize()
+    for index, (a, out) in enumerate(zip(inputs, outputs)):
+        check(oracle, out, a, b, None, 1.0, 0.0, f"overlapping call {index}")
+    # join(): the current stream waits for the copy-outs, so an event recorded on it comes after them.
+    out = torch.full((m, n), float("nan")).pin_memory()
+    pipeline(inputs[0], b, out=out, overlap_calls=True)
+    pipeline.join()
+    torch.cuda.current_stream().synchronize()
+    check(oracle, out, inputs[0], b, None, 1.0, 0.0, "joined call")
+
+
 def test_one_shot_form_and_checks(binding, oracle):
     a = torch.randn(130, 64).pin_memory()
     b = torch.randn(64, 72).pin_memory()
