@@ -11,10 +11,12 @@
 namespace ftrain {
 
 std::vector<std::shared_ptr<OpsEngineBase>> makeBuiltinOpsEngines() {
-    // The reference registers the Gemm engine only; the GroupedABCDGemm engine is this build's addition
-    // (its other two grouped operations, with TensorList operands, stay without one, as there).
+    // The reference registers the Gemm engine only; the three grouped-GEMM engines are this build's addition
+    // (its public API declares the operations, include/flash_train/common.h:248-306 there).
     return {std::make_shared<OpsEngine<GemmFamily, B200Heuristic, RegistrationOrderFinder>>(),
-            std::make_shared<OpsEngine<GroupedGemmFamily, GroupedB200Heuristic>>()};
+            std::make_shared<OpsEngine<GroupedGemmFamily, GroupedB200Heuristic>>(),
+            std::make_shared<OpsEngine<GroupedBcdGemmFamily, GroupedB200Heuristic>>(),
+            std::make_shared<OpsEngine<GroupedAbGemmFamily, GroupedB200Heuristic>>()};
 }
 
 }  // namespace ftrain

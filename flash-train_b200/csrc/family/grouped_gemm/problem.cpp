@@ -3,6 +3,7 @@
 #include <cstring>
 #include <limits>
 #include <utility>
+#include <variant>
 
 #include "core/error.hpp"
 
@@ -55,80 +56,132 @@ bool productOverflows(std::uint64_t x, std::uint64_t y) noexcept {
     return y != 0 && x > std::numeric_limits<std::uint64_t>::max() / sizeof(float) / y;
 }
 
+bool floatAligned(const void* address) noexcept { return reinterpret_cast<std::uintptr_t>(address) % alignof(float) == 0; }
+
+void checkExtents(const GroupMatrix& matrix, std::uint32_t group, const char* port) {
+    if (matrix.rows < 0 || matrix.cols < 0) {
+        throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: group %u of %s has a negative extent", static_cast<unsigned>(group), port);
+    }
+    if (productOverflows(static_cast<std::uint64_t>(matrix.rows), static_cast<std::uint64_t>(matrix.cols))) {
+        throw Exception(FTRAIN_STATUS_OVERFLOW, "GroupedGemm: the byte size of group %u of %s does not fit 64 bits",
+                        static_cast<unsigned>(group), port);
+    }
+}
+
+GroupedOperand decodeGrouped(const GroupedTensor& tensor, const char* port) {
+    GroupedOperand operand;
+    const StorageView& data = tensor.getData();
+    if (data.getDims().size() != 2) {
+        throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: a, b, c and d must be rank two (%s is not)", port);
+    }
+    if (tensor.getDimSizes().size() != 2) {
+        throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: %s needs dim_sizes for both dimensions", port);
+    }
+    const bool strided  = tensor.getStrides().size() == 2;
+    const bool has_base = tensor.getOffsets().has_value();
+    if (!has_base && data.getIndexType() != FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS) {
+        throw Exception(FTRAIN_STATUS_UNSUPPORTED, "GroupedGemm: %s has no offsets and its data is not indexed GROUPED_CONTINUOUS", port);
+    }
+    operand.is_list          = false;
+    operand.numeric_type     = data.getNumericType();
+    operand.plainly_indexed  = data.getIndexType() == FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS || data.getIndexType() == FTRAIN_INDEX_TYPE_CONTINUOUS;
+    operand.in_device_memory = !data.isHostMemory();
+    operand.any_memory       = data.getMemory() != nullptr;
+    operand.all_memory       = data.getMemory() != nullptr;
+    operand.float_aligned    = floatAligned(data.getMemory());
+    operand.groups.resize(tensor.getNumGroups());
+    std::int64_t running = 0;  // dense packing when no offsets are given
+    for (std::uint32_t g = 0; g < tensor.getNumGroups(); ++g) {
+        GroupMatrix& matrix = operand.groups[g];
+        matrix.base         = data.getMemory();
+        matrix.rows         = readEntry(tensor.getDimSizes()[0], g, port, "dim_sizes[0]");
+        matrix.cols         = readEntry(tensor.getDimSizes()[1], g, port, "dim_sizes[1]");
+        checkExtents(matrix, g, port);
+        matrix.row_stride = strided ? readEntry(tensor.getStrides()[0], g, port, "strides[0]") : matrix.cols;
+        matrix.col_stride = strided ? readEntry(tensor.getStrides()[1], g, port, "strides[1]") : 1;
+        matrix.offset     = has_base ? readEntry(*tensor.getOffsets(), g, port, "offsets") : running;
+        if (matrix.offset < 0) {
+            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: group %u of %s has a negative offset", static_cast<unsigned>(g), port);
+        }
+        running += matrix.rows * matrix.cols;
+    }
+    return operand;
+}
+
+GroupedOperand decodeList(const TensorList& list, const char* port) {
+    GroupedOperand operand;
+    const std::vector<StorageView>& views = list.getStorageViews();
+    operand.is_list    = true;
+    operand.all_memory = true;
+    operand.groups.resize(views.size());
+    for (std::size_t g = 0; g < views.size(); ++g) {
+        const StorageView& view = views[g];
+        if (view.getDims().size() != 2) {
+            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: a, b, c and d must be rank two (entry %zu of %s is not)", g, port);
+        }
+        GroupMatrix& matrix = operand.groups[g];
+        matrix.base         = view.getMemory();
+        matrix.offset       = 0;
+        matrix.rows         = view.getDims()[0];
+        matrix.cols         = view.getDims()[1];
+        checkExtents(matrix, static_cast<std::uint32_t>(g), port);
+        const bool strided = view.getIndexType() == FTRAIN_INDEX_TYPE_INVALID && view.getStrides().size() == 2;
+        matrix.row_stride  = strided ? view.getStrides()[0] : matrix.cols;
+        matrix.col_stride  = strided ? view.getStrides()[1] : 1;
+        if (g == 0) {
+            operand.numeric_type = view.getNumericType();
+        } else if (operand.numeric_type != view.getNumericType()) {
+            operand.numeric_type = FTRAIN_NUMERIC_TYPE_INVALID;
+        }
+        operand.plainly_indexed  = operand.plainly_indexed && (strided || view.getIndexType() == FTRAIN_INDEX_TYPE_CONTINUOUS);
+        operand.in_device_memory = operand.in_device_memory && !view.isHostMemory();
+        operand.any_memory       = operand.any_memory || view.getMemory() != nullptr;
+        operand.all_memory       = operand.all_memory && (view.getMemory() != nullptr || matrix.rows * matrix.cols == 0);
+        operand.float_aligned    = operand.float_aligned && floatAligned(view.getMemory());
+    }
+    if (views.empty()) { operand.numeric_type = FTRAIN_NUMERIC_TYPE_FP32; }  // nothing to disagree with
+    return operand;
+}
+
+GroupedOperand decode(const OperandValue& value, const char* port) {
+    if (const GroupedTensor* grouped = std::get_if<GroupedTensor>(&value)) { return decodeGrouped(*grouped, port); }
+    if (const TensorList* list = std::get_if<TensorList>(&value)) { return decodeList(*list, port); }
+    throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: %s must be a GroupedTensor or a TensorList", port);
+}
+
 }  // namespace
 
-GroupedGemmProblem::GroupedGemmProblem(GroupedTensor a, GroupedTensor b, GroupedTensor c, GroupedTensor d, Tensor alpha,
-                                       Tensor beta, FTrainNumericType compute_type)
-    : tensors_{std::move(a), std::move(b), std::move(c), std::move(d)}, alpha_(std::move(alpha)), beta_(std::move(beta)),
-      compute_type_(compute_type), num_groups_(tensors_[0].getNumGroups()) {
-    for (int port = 0; port < 4; ++port) {
-        const GroupedTensor& tensor = tensors_[port];
-        if (tensor.getData().getDims().size() != 2) {
-            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: a, b, c and d must be rank-two GroupedTensors");
-        }
-        if (tensor.getNumGroups() != num_groups_) {
-            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: %s has %u groups but a has %u", kPortNames[port],
-                            static_cast<unsigned>(tensor.getNumGroups()), static_cast<unsigned>(num_groups_));
+GroupedGemmProblem::GroupedGemmProblem(const OperandValue& a, const OperandValue& b, const OperandValue& c, const OperandValue& d,
+                                       Tensor alpha, Tensor beta, FTrainNumericType compute_type)
+    : operands_{decode(a, "a"), decode(b, "b"), decode(c, "c"), decode(d, "d")}, alpha_(std::move(alpha)), beta_(std::move(beta)),
+      compute_type_(compute_type) {
+    num_groups_ = static_cast<std::uint32_t>(operands_[0].groups.size());
+    for (int port = 1; port < 4; ++port) {
+        if (operands_[port].groups.size() != num_groups_) {
+            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: %s has %zu groups but a has %u", kPortNames[port],
+                            operands_[port].groups.size(), static_cast<unsigned>(num_groups_));
         }
     }
     if (!alpha_.getStorageView().getDims().empty() || !beta_.getStorageView().getDims().empty()) {
         throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: alpha and beta must be scalars (rank zero)");
     }
     for (int port = 0; port < 4; ++port) {
-        if (tensors_[port].getData().isHostMemory()) {
+        if (!operands_[port].in_device_memory) {
             throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: the data of a, b, c and d must live in device memory");
         }
     }
     if (!alpha_.getStorageView().isHostMemory() || !beta_.getStorageView().isHostMemory()) {
         throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: alpha and beta must live in host memory");
     }
-
-    // Decode the per-group metadata once; the kernels' tile lists and the key are made from it.
-    for (int port = 0; port < 4; ++port) {
-        const GroupedTensor& tensor = tensors_[port];
-        if (tensor.getDimSizes().size() != 2) {
-            throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: %s needs dim_sizes for both dimensions", kPortNames[port]);
-        }
-        const bool strided  = tensor.getStrides().size() == 2;
-        const bool has_base = tensor.getOffsets().has_value();
-        if (!has_base && tensor.getData().getIndexType() != FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS) {
-            throw Exception(FTRAIN_STATUS_UNSUPPORTED,
-                            "GroupedGemm: %s has no offsets and its data is not indexed GROUPED_CONTINUOUS", kPortNames[port]);
-        }
-        std::vector<GroupMatrix>& groups = groups_[port];
-        groups.resize(num_groups_);
-        std::int64_t running = 0;  // dense packing when no offsets are given
-        for (std::uint32_t g = 0; g < num_groups_; ++g) {
-            GroupMatrix& matrix = groups[g];
-            matrix.rows         = readEntry(tensor.getDimSizes()[0], g, kPortNames[port], "dim_sizes[0]");
-            matrix.cols         = readEntry(tensor.getDimSizes()[1], g, kPortNames[port], "dim_sizes[1]");
-            if (matrix.rows < 0 || matrix.cols < 0) {
-                throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: group %u of %s has a negative extent",
-                                static_cast<unsigned>(g), kPortNames[port]);
-            }
-            if (productOverflows(static_cast<std::uint64_t>(matrix.rows), static_cast<std::uint64_t>(matrix.cols))) {
-                throw Exception(FTRAIN_STATUS_OVERFLOW, "GroupedGemm: the byte size of group %u of %s does not fit 64 bits",
-                                static_cast<unsigned>(g), kPortNames[port]);
-            }
-            matrix.row_stride = strided ? readEntry(tensor.getStrides()[0], g, kPortNames[port], "strides[0]") : matrix.cols;
-            matrix.col_stride = strided ? readEntry(tensor.getStrides()[1], g, kPortNames[port], "strides[1]") : 1;
-            matrix.offset     = has_base ? readEntry(*tensor.getOffsets(), g, kPortNames[port], "offsets") : running;
-            if (matrix.offset < 0) {
-                throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: group %u of %s has a negative offset",
-                                static_cast<unsigned>(g), kPortNames[port]);
-            }
-            running += matrix.rows * matrix.cols;
-        }
-    }
     for (std::uint32_t g = 0; g < num_groups_; ++g) {
-        const GroupMatrix& ga = groups_[0][g];
-        const GroupMatrix& gb = groups_[1][g];
+        const GroupMatrix& ga = operands_[0].groups[g];
+        const GroupMatrix& gb = operands_[1].groups[g];
         if (ga.cols != gb.rows) {
             throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: in group %u a has %lld columns but b has %lld rows",
                             static_cast<unsigned>(g), static_cast<long long>(ga.cols), static_cast<long long>(gb.rows));
         }
         for (const int port : {2, 3}) {
-            const GroupMatrix& out = groups_[port][g];
+            const GroupMatrix& out = operands_[port].groups[g];
             if (out.rows != ga.rows || out.cols != gb.cols) {
                 throw Exception(FTRAIN_STATUS_INVALID_ARGUMENT, "GroupedGemm: in group %u %s must be %lld-by-%lld like the product of a and b",
                                 static_cast<unsigned>(g), kPortNames[port], static_cast<long long>(ga.rows),
@@ -140,25 +193,23 @@ GroupedGemmProblem::GroupedGemmProblem(GroupedTensor a, GroupedTensor b, Grouped
 }
 
 bool GroupedGemmProblem::isInPlace() const noexcept {
-    if (getData(GroupedPort::kC).getMemory() != getData(GroupedPort::kD).getMemory()) { return false; }
     for (std::uint32_t g = 0; g < num_groups_; ++g) {
-        if (groups_[2][g].offset != groups_[3][g].offset) { return false; }
+        if (operands_[2].groups[g].address() != operands_[3].groups[g].address()) { return false; }
     }
     return true;
 }
 
 std::vector<std::uint64_t> GroupedGemmProblem::getProblemKey() const {
     std::vector<std::uint64_t> key;
-    key.reserve(4 * (3 + 5 * static_cast<std::size_t>(num_groups_)) + 3);
+    key.reserve(4 * (2 + 6 * static_cast<std::size_t>(num_groups_)) + 5);
     key.push_back(num_groups_);
-    for (int port = 0; port < 4; ++port) {
-        const StorageView& data = tensors_[port].getData();
-        const void* memory      = data.getMemory();
-        key.push_back(static_cast<std::uint64_t>(data.getNumericType()) | static_cast<std::uint64_t>(data.getIndexType()) << 8);
-        key.push_back(memory != nullptr ? 1U : 0U);
-        key.push_back(memory != nullptr ? reinterpret_cast<std::uintptr_t>(memory) & 15U : 0U);
-        for (const GroupMatrix& matrix : groups_[port]) {
-            for (const std::int64_t value : {matrix.offset, matrix.rows, matrix.cols, matrix.row_stride, matrix.col_stride}) {
+    for (const GroupedOperand& operand : operands_) {
+        key.push_back((operand.is_list ? 1U : 0U) | static_cast<std::uint64_t>(operand.numeric_type) << 8 |
+                      (operand.plainly_indexed ? 1ULL << 16 : 0ULL) | (operand.float_aligned ? 1ULL << 17 : 0ULL));
+        for (const GroupMatrix& matrix : operand.groups) {
+            const float* address = matrix.address();
+            key.push_back(address != nullptr ? 1U + ((reinterpret_cast<std::uintptr_t>(address) & 15U) << 1) : 0U);
+            for (const std::int64_t value : {matrix.rows, matrix.cols, matrix.row_stride, matrix.col_stride}) {
                 key.push_back(static_cast<std::uint64_t>(value));
             }
         }

@@ -10,8 +10,7 @@ constexpr GroupedPort kPorts[] = {GroupedPort::kA, GroupedPort::kB, GroupedPort:
 bool floatAligned(const void* address) noexcept { return reinterpret_cast<std::uintptr_t>(address) % alignof(float) == 0; }
 
 const float* groupAddress(const GroupedGemmProblem& problem, GroupedPort port, std::uint32_t group) noexcept {
-    const float* base = static_cast<const float*>(problem.getData(port).getMemory());
-    return base == nullptr ? nullptr : base + problem.getGroup(port, group).offset;
+    return problem.getGroup(port, group).address();
 }
 
 }  // namespace
@@ -63,16 +62,10 @@ std::vector<FtcudaGemmDesc> makeCudaGroupedDescs(const GroupedGemmProblem& probl
 Result CudaGroupedGemm::isApplicable(const GroupedGemmProblem& problem, const Constraints& constraints) const {
     if (problem.getComputeType() != FTRAIN_NUMERIC_TYPE_FP32) { return Result(FTRAIN_STATUS_UNSUPPORTED, "compute type is not fp32"); }
     for (const GroupedPort port : kPorts) {
-        if (problem.getData(port).getNumericType() != FTRAIN_NUMERIC_TYPE_FP32) {
-            return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand is not fp32");
-        }
-        const FTrainIndexType index_type = problem.getData(port).getIndexType();
-        if (index_type != FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS && index_type != FTRAIN_INDEX_TYPE_CONTINUOUS) {
-            return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand's data is not continuously indexed");
-        }
-        if (!floatAligned(problem.getData(port).getMemory())) {
-            return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand address is not float-aligned");
-        }
+        const GroupedOperand& operand = problem.getOperand(port);
+        if (operand.numeric_type != FTRAIN_NUMERIC_TYPE_FP32) { return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand is not fp32"); }
+        if (!operand.plainly_indexed) { return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand's data is not continuously indexed"); }
+        if (!operand.float_aligned) { return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand address is not float-aligned"); }
     }
     for (const StorageView* scalar : {&problem.getAlpha(), &problem.getBeta()}) {
         if (scalar->getNumericType() != FTRAIN_NUMERIC_TYPE_FP32) { return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand is not fp32"); }
@@ -82,14 +75,16 @@ Result CudaGroupedGemm::isApplicable(const GroupedGemmProblem& problem, const Co
         if (!floatAligned(scalar->getMemory())) { return Result(FTRAIN_STATUS_UNSUPPORTED, "an operand address is not float-aligned"); }
     }
     if (!problem.hasEmptyOutput()) {
-        bool depth = false;  // does any group with output multiply anything?
+        // d needs an address wherever it has elements, a and b wherever they are multiplied. A group whose
+        // c has no address simply has no beta * C term.
+        bool addressed = true;
         for (std::uint32_t g = 0; g < problem.getNumGroups(); ++g) {
             const GroupMatrix& a = problem.getGroup(GroupedPort::kA, g);
-            depth                = depth || (a.rows != 0 && a.cols != 0 && problem.getGroup(GroupedPort::kB, g).cols != 0);
+            const GroupMatrix& b = problem.getGroup(GroupedPort::kB, g);
+            if (a.rows * b.cols == 0) { continue; }
+            addressed = addressed && problem.getGroup(GroupedPort::kD, g).base != nullptr;
+            if (a.cols != 0) { addressed = addressed && a.base != nullptr && b.base != nullptr; }
         }
-        const bool addressed = problem.getData(GroupedPort::kD).getMemory() != nullptr &&
-                               (!depth || (problem.getData(GroupedPort::kA).getMemory() != nullptr &&
-                                           problem.getData(GroupedPort::kB).getMemory() != nullptr));
         if (!addressed) { return Result(FTRAIN_STATUS_UNSUPPORTED, "a required operand address is null"); }
     }
     const std::vector<FtcudaGemmDesc> descs = makeCudaGroupedDescs(problem, constraints.getDeviceId(), false);

@@ -261,8 +261,15 @@ class Args(_Handle):
                                                        byref(offsets) if offsets is not None else None,
                                                        array(dim_sizes), array(strides)))
 
+    def set_tensor_list(self, role: RoleId, views) -> None:
+        array = (StorageView * max(len(views), 1))(*views)
+        self.check(self.lib.ftrainArgsSetTensorList(self.handle, role, array if views else None, len(views)))
+
+    def set_grouped_gemm(self, op: RoleId, kind: str = "GroupedABCDGemm", compute_type: int = NUMERIC_FP32) -> None:
+        self.check(getattr(self.lib, f"ftrainArgsSet{kind}")(self.handle, op, compute_type))
+
     def set_grouped_abcd_gemm(self, op: RoleId, compute_type: int = NUMERIC_FP32) -> None:
-        self.check(self.lib.ftrainArgsSetGroupedABCDGemm(self.handle, op, compute_type))
+        self.set_grouped_gemm(op, "GroupedABCDGemm", compute_type)
 
 
 class Plan(_Handle):
@@ -341,25 +348,36 @@ class GemmBinding:
 
 
 class GroupedGemmBinding:
-    """Pattern -> Ops for the GroupedABCDGemm graph (four GroupedTensors, two scalars), plus a Plan factory.
+    """Pattern -> Ops for one of the grouped GEMM graphs, plus a Plan factory.
 
-    A grouped operand is given as (address of the data, rows per group, columns per group) with
-    optional per-group element offsets and (row, column) element strides; without them the groups
-    are dense row-major matrices stored one after another. The per-group arrays are passed to the
-    library as int64 host arrays, which it reads while the Plan is made.
+    kind "GroupedABCDGemm": a, b, c, d are GroupedTensors; "GroupedBCDGemm": a is a TensorList;
+    "GroupedABGemm": c and d are TensorLists.
+
+    A GroupedTensor operand is given as a dict {address, rows, cols[, offsets, row_strides, col_strides]}
+    (per-group lists; without offsets / strides the groups are dense row-major matrices stored one after
+    another) and reaches the library as int64 host arrays, which it reads while the Plan is made. A
+    TensorList operand is given as a list of (address, (rows, cols), strides-or-None), one entry per group.
     """
 
-    def __init__(self, order=("a", "b", "c", "alpha", "beta", "d"), lib=lib):
+    LIST_ROLES = {"GroupedABCDGemm": (), "GroupedBCDGemm": ("a",), "GroupedABGemm": ("c", "d")}
+
+    def __init__(self, order=("a", "b", "c", "alpha", "beta", "d"), kind="GroupedABCDGemm", lib=lib):
         pattern = Pattern(lib)
-        grouped = {"a", "b", "c", "d"}
-        self.roles = {name: (pattern.add_grouped_tensor() if name in grouped else pattern.add_tensor()) for name in order}
+        self.kind = kind
+        self.lists = set(self.LIST_ROLES[kind])
+
+        def add(name):
+            if name in ("alpha", "beta"):
+                return pattern.add_tensor()
+            return pattern.add_tensor_list() if name in self.lists else pattern.add_grouped_tensor()
+
+        self.roles = {name: add(name) for name in order}
         r = self.roles
-        self.gemm = pattern.add_gemm(r["a"], r["b"], r["c"], r["d"], r["alpha"], r["beta"], kind="GroupedABCDGemm")
+        self.gemm = pattern.add_gemm(r["a"], r["b"], r["c"], r["d"], r["alpha"], r["beta"], kind=kind)
         self.ops = Ops(pattern)
         pattern.close()
 
     def make_plan(self, a, b, c, d, alpha: float = 1.0, beta: float = 0.0, compute_type: int = NUMERIC_FP32) -> "Plan":
-        """a, b, c, d: dicts with keys address, rows, cols and optionally offsets, row_strides, col_strides."""
         args = Args(self.ops)
         keep = []
 
@@ -370,6 +388,14 @@ class GroupedGemmBinding:
             return view
 
         for name, operand in (("a", a), ("b", b), ("c", c), ("d", d)):
+            if name in self.lists:
+                views = []
+                for address, dims, strides in operand:
+                    view, alive = make_view(address, dims, strides)
+                    keep.append(alive)
+                    views.append(view)
+                args.set_tensor_list(self.roles[name], views)
+                continue
             groups = len(operand["rows"])
             data, alive = make_view(operand["address"], (0, 0), index_type=INDEX_GROUPED_CONTINUOUS)
             keep.append(alive)
@@ -384,7 +410,7 @@ class GroupedGemmBinding:
             view, alive = make_view(ctypes.addressof(scalars) + 4 * index, (), host=True)
             keep.append(alive)
             args.set_tensor(self.roles[name], view)
-        args.set_grouped_abcd_gemm(self.gemm, compute_type)
+        args.set_grouped_gemm(self.gemm, self.kind, compute_type)
         plan = Plan(args)
         args.close()
         del keep

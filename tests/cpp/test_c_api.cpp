@@ -96,19 +96,15 @@ TEST(ops_create_validates_and_matches) {
     CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, bad)), static_cast<int>(FTRAIN_STATUS_INVALID_ARGUMENT));
     CHECK(ops == nullptr);
     ftrainPatternDestroy(bad);
-    // A graph no engine supports (a grouped GEMM whose c and d are TensorLists has none, here as in the
-    // reference): UNSUPPORTED, the caller's variable unchanged.
+    // A graph no engine supports (two Gemm nodes chained through one matrix): UNSUPPORTED, the caller's
+    // variable unchanged.
     FTrainPattern unsupported = nullptr;
     ftrainPatternCreate(&unsupported);
-    FTrainGroupedTensorId g[2];
-    for (auto& id : g) { ftrainPatternAddGroupedTensor(unsupported, &id); }
-    FTrainTensorListId lists[2];
-    for (auto& id : lists) { ftrainPatternAddTensorList(unsupported, &id); }
-    FTrainTensorId alpha, beta;
-    ftrainPatternAddTensor(unsupported, &alpha);
-    ftrainPatternAddTensor(unsupported, &beta);
-    FTrainGroupedABGemmOpId list_op;
-    CHECK_EQ(static_cast<int>(ftrainPatternAddGroupedABGemm(unsupported, &list_op, g[0], g[1], lists[0], lists[1], alpha, beta)), 0);
+    FTrainTensorId n[10];
+    for (auto& id : n) { ftrainPatternAddTensor(unsupported, &id); }
+    FTrainGemmOpId first_op, second_op;
+    CHECK_EQ(static_cast<int>(ftrainPatternAddGemm(unsupported, &first_op, n[0], n[1], n[2], n[3], n[4], n[5])), 0);
+    CHECK_EQ(static_cast<int>(ftrainPatternAddGemm(unsupported, &second_op, n[3], n[6], n[7], n[8], n[4], n[5])), 0);
     CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, unsupported)), static_cast<int>(FTRAIN_STATUS_UNSUPPORTED));
     CHECK(ops == nullptr);
     ftrainPatternDestroy(unsupported);

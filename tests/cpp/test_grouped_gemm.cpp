@@ -65,7 +65,8 @@ struct Ragged {
     GroupedSpec c{address(0x1100000), {256, 0, 130}, {384, 384, 200}};
     GroupedSpec d{address(0x1900000), {256, 0, 130}, {384, 384, 200}};
     GroupedGemmProblem problem(FTrainNumericType compute = FTRAIN_NUMERIC_TYPE_FP32) {
-        return GroupedGemmProblem(grouped(a), grouped(b), grouped(c), grouped(d), scalar(&g_alpha), scalar(&g_beta), compute);
+        return GroupedGemmProblem(OperandValue(grouped(a)), OperandValue(grouped(b)), OperandValue(grouped(c)), OperandValue(grouped(d)),
+                                  scalar(&g_alpha), scalar(&g_beta), compute);
     }
 };
 
@@ -99,8 +100,8 @@ TEST(grouped_problem_decodes_dense_and_explicit_layouts) {
                                                        FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS, false}),
                       std::nullopt, std::move(dims32), {});
     Ragged other;
-    const GroupedGemmProblem mixed(std::move(a32), grouped(other.b), grouped(other.c), grouped(other.d), scalar(&g_alpha), scalar(&g_beta),
-                                   FTRAIN_NUMERIC_TYPE_FP32);
+    const GroupedGemmProblem mixed(OperandValue(std::move(a32)), OperandValue(grouped(other.b)), OperandValue(grouped(other.c)),
+                                   OperandValue(grouped(other.d)), scalar(&g_alpha), scalar(&g_beta), FTRAIN_NUMERIC_TYPE_FP32);
     CHECK_EQ(mixed.getGroup(GroupedPort::kA, 2).offset, std::int64_t{256 * 512});
     CHECK(mixed.getProblemKey() == dense.getProblemKey());
     // c and d on the same memory with the same offsets: in place.
@@ -152,8 +153,8 @@ TEST(grouped_problem_validation_statuses) {
     }
     {
         Ragged r;  // alpha in device memory
-        CHECK_THROWS_STATUS(GroupedGemmProblem(grouped(r.a), grouped(r.b), grouped(r.c), grouped(r.d), scalar(&g_alpha, false),
-                                               scalar(&g_beta), FTRAIN_NUMERIC_TYPE_FP32),
+        CHECK_THROWS_STATUS(GroupedGemmProblem(OperandValue(grouped(r.a)), OperandValue(grouped(r.b)), OperandValue(grouped(r.c)),
+                                               OperandValue(grouped(r.d)), scalar(&g_alpha, false), scalar(&g_beta), FTRAIN_NUMERIC_TYPE_FP32),
                             FTRAIN_STATUS_INVALID_ARGUMENT);
     }
 }
@@ -200,7 +201,9 @@ TEST(grouped_engine_is_registered_and_selects_best_first) {
     fake::reset();
     const auto engine = getGlobalHandle().findOpsEngine(GroupedGemmFamily::getRoles().pattern.getKey());
     CHECK(engine != nullptr);
-    CHECK_EQ(getGlobalHandle().getNumOpsEngines(), std::size_t{2});
+    CHECK(getGlobalHandle().findOpsEngine(GroupedBcdGemmFamily::getRoles().pattern.getKey()) != nullptr);
+    CHECK(getGlobalHandle().findOpsEngine(GroupedAbGemmFamily::getRoles().pattern.getKey()) != nullptr);
+    CHECK_EQ(getGlobalHandle().getNumOpsEngines(), std::size_t{4});
 }
 
 // Through the public C API: Pattern with the roles in a foreign order -> Ops -> Args -> Plan -> execute.
@@ -307,5 +310,116 @@ TEST(grouped_gemm_with_only_empty_groups_plans_and_runs_nothing) {
     CHECK_EQ(exact.getRequiredWorkspaceBytes(), std::uint64_t{0});
     exact.execute(Resources(nullptr, 0, nullptr));
     CHECK_EQ(fake::state().grouped_launches.size(), std::size_t{0});
+    fake::reset();
+}
+
+// GroupedBCDGemm (a is a TensorList) and GroupedABGemm (c and d are TensorLists): a list's g-th view is group g,
+// an ordinary matrix view with its own address, extents and (optional) strides.
+TEST(grouped_problem_takes_tensor_lists) {
+    Ragged ragged;
+    const std::int64_t dims[3][2]  = {{256, 512}, {0, 512}, {130, 260}};
+    const std::int64_t pitch[2]    = {264, 1};  // group 2 of a lives in a wider buffer
+    std::vector<StorageView> a_views;
+    a_views.emplace_back(FTrainStorageView{address(0x100000), dims[0], nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_CONTINUOUS, false});
+    a_views.emplace_back(FTrainStorageView{nullptr, dims[1], nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_CONTINUOUS, false});
+    a_views.emplace_back(FTrainStorageView{address(0x300010), dims[2], pitch, 2, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_INVALID, false});
+    const GroupedGemmProblem bcd(OperandValue(TensorList(std::vector<StorageView>(a_views))), OperandValue(grouped(ragged.b)),
+                                 OperandValue(grouped(ragged.c)), OperandValue(grouped(ragged.d)), scalar(&g_alpha), scalar(&g_beta),
+                                 FTRAIN_NUMERIC_TYPE_FP32);
+    CHECK(bcd.getOperand(GroupedPort::kA).is_list && !bcd.getOperand(GroupedPort::kB).is_list);
+    CHECK(bcd.getGroup(GroupedPort::kA, 2).address() == static_cast<const float*>(address(0x300010)));
+    CHECK_EQ(bcd.getGroup(GroupedPort::kA, 2).row_stride, std::int64_t{264});
+    CHECK_EQ(bcd.getGroup(GroupedPort::kA, 0).row_stride, std::int64_t{512});
+    const CudaGroupedGemm exact(FTCUDA_GROUPED_GEMM_EXACT);
+    CHECK(exact.isApplicable(bcd, Constraints{0}).isSuccess());  // the empty group's a needs no address
+    const std::vector<FtcudaGemmDesc> descs = makeCudaGroupedDescs(bcd, 0, true);
+    CHECK(descs[2].a == static_cast<const float*>(address(0x300010)));
+    CHECK_EQ(descs[2].a_row_stride, std::int64_t{264});
+    // Another list length than the other operands' group count: contradictory.
+    a_views.pop_back();
+    CHECK_THROWS_STATUS(GroupedGemmProblem(OperandValue(TensorList(std::move(a_views))), OperandValue(grouped(ragged.b)),
+                                           OperandValue(grouped(ragged.c)), OperandValue(grouped(ragged.d)), scalar(&g_alpha), scalar(&g_beta),
+                                           FTRAIN_NUMERIC_TYPE_FP32),
+                        FTRAIN_STATUS_INVALID_ARGUMENT);
+    // A list mixing numeric types is not something a Primitive takes.
+    const std::int64_t cd_dims[3][2] = {{256, 384}, {0, 384}, {130, 200}};
+    std::vector<StorageView> c_views, d_views;
+    for (int g = 0; g < 3; ++g) {
+        c_views.emplace_back(FTrainStorageView{address(0x1100000 + 0x100000 * g), cd_dims[g], nullptr, 2,
+                                               g == 1 ? FTRAIN_NUMERIC_TYPE_FP16 : FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_CONTINUOUS, false});
+        d_views.emplace_back(FTrainStorageView{address(0x1900000 + 0x100000 * g), cd_dims[g], nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32,
+                                               FTRAIN_INDEX_TYPE_CONTINUOUS, false});
+    }
+    const GroupedGemmProblem ab(OperandValue(grouped(ragged.a)), OperandValue(grouped(ragged.b)), OperandValue(TensorList(std::move(c_views))),
+                                OperandValue(TensorList(std::move(d_views))), scalar(&g_alpha), scalar(&g_beta), FTRAIN_NUMERIC_TYPE_FP32);
+    CHECK(std::strstr(exact.isApplicable(ab, Constraints{0}).getMessage(), "an operand is not fp32") != nullptr);
+    // A plain Tensor where a grouped operand belongs.
+    CHECK_THROWS_STATUS(GroupedGemmProblem(OperandValue(scalar(&g_alpha)), OperandValue(grouped(ragged.b)), OperandValue(grouped(ragged.c)),
+                                           OperandValue(grouped(ragged.d)), scalar(&g_alpha), scalar(&g_beta), FTRAIN_NUMERIC_TYPE_FP32),
+                        FTRAIN_STATUS_INVALID_ARGUMENT);
+}
+
+TEST(grouped_ab_gemm_through_the_c_api) {
+    fake::reset();
+    FTrainPattern pattern = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainPatternCreate(&pattern)), 0);
+    FTrainGroupedTensorId a, b;
+    FTrainTensorListId c, d;
+    FTrainTensorId alpha, beta;
+    ftrainPatternAddTensorList(pattern, &d);
+    ftrainPatternAddGroupedTensor(pattern, &a);
+    ftrainPatternAddTensor(pattern, &alpha);
+    ftrainPatternAddTensorList(pattern, &c);
+    ftrainPatternAddGroupedTensor(pattern, &b);
+    ftrainPatternAddTensor(pattern, &beta);
+    FTrainGroupedABGemmOpId op;
+    CHECK_EQ(static_cast<int>(ftrainPatternAddGroupedABGemm(pattern, &op, a, b, c, d, alpha, beta)), 0);
+    FTrainOps ops = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainOpsCreate(&ops, pattern)), 0);
+    ftrainPatternDestroy(pattern);
+    FTrainArgs args = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainArgsCreate(&args, ops)), 0);
+    Ragged ragged;
+    const std::int64_t count = 3, whole[2] = {0, 0};
+    const auto set = [&](FTrainGroupedTensorId role, const GroupedSpec& spec) {
+        const FTrainStorageView data{spec.data, whole, nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_GROUPED_CONTINUOUS, false};
+        const FTrainStorageView dims[2] = {spec.vector(spec.rows, &count), spec.vector(spec.cols, &count)};
+        return ftrainArgsSetGroupedTensor(args, role, 3, data, nullptr, dims, nullptr);
+    };
+    CHECK_EQ(static_cast<int>(set(a, ragged.a)), 0);
+    CHECK_EQ(static_cast<int>(set(b, ragged.b)), 0);
+    const std::int64_t cd_dims[3][2] = {{256, 384}, {0, 384}, {130, 200}};
+    FTrainStorageView c_views[3], d_views[3];
+    for (int g = 0; g < 3; ++g) {
+        c_views[g] = FTrainStorageView{g == 2 ? nullptr : address(0x1100000 + 0x100000 * g), cd_dims[g], nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32,
+                                       FTRAIN_INDEX_TYPE_CONTINUOUS, false};  // group 2 has no addend
+        d_views[g] = FTrainStorageView{address(0x1900000 + 0x100000 * g), cd_dims[g], nullptr, 2, FTRAIN_NUMERIC_TYPE_FP32,
+                                       FTRAIN_INDEX_TYPE_CONTINUOUS, false};
+    }
+    CHECK_EQ(static_cast<int>(ftrainArgsSetTensorList(args, c, c_views, 3)), 0);
+    CHECK_EQ(static_cast<int>(ftrainArgsSetTensorList(args, d, d_views, 3)), 0);
+    const FTrainStorageView alpha_view{&g_alpha, nullptr, nullptr, 0, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_CONTINUOUS, true};
+    const FTrainStorageView beta_view{&g_beta, nullptr, nullptr, 0, FTRAIN_NUMERIC_TYPE_FP32, FTRAIN_INDEX_TYPE_CONTINUOUS, true};
+    CHECK_EQ(static_cast<int>(ftrainArgsSetTensor(args, alpha, alpha_view)), 0);
+    CHECK_EQ(static_cast<int>(ftrainArgsSetTensor(args, beta, beta_view)), 0);
+    // The other operations' setters do not fit this role.
+    CHECK_EQ(static_cast<int>(ftrainArgsSetGroupedABCDGemm(args, FTrainGroupedABCDGemmOpId{op.opaque}, FTRAIN_NUMERIC_TYPE_FP32)),
+             static_cast<int>(FTRAIN_STATUS_INVALID_ARGUMENT));
+    CHECK_EQ(static_cast<int>(ftrainArgsSetGroupedABGemm(args, op, FTRAIN_NUMERIC_TYPE_FP32)), 0);
+    FTrainPlan plan = nullptr;
+    CHECK_EQ(static_cast<int>(ftrainPlanCreate(&plan, args)), 0);
+    const char* name = nullptr;
+    ftrainPlanGetPrimitiveName(plan, 0, &name);
+    CHECK_EQ(std::string(name), std::string("GroupedFp32Gemm3xTf32"));
+    char workspace[8];
+    CHECK_EQ(static_cast<int>(ftrainPlanExecutePrimitive(plan, 0, workspace, 4096, nullptr)), 0);
+    const fake::GroupedLaunchRecord& launched = fake::state().grouped_launches.back();
+    CHECK(launched.groups[0].c == static_cast<const float*>(address(0x1100000)));
+    CHECK(launched.groups[2].c == nullptr);
+    CHECK(launched.groups[2].d == static_cast<float*>(address(0x1b00000)));
+    CHECK_EQ(launched.groups[2].d_row_stride, std::int64_t{200});
+    ftrainPlanDestroy(plan);
+    ftrainArgsDestroy(args);
+    ftrainOpsDestroy(ops);
     fake::reset();
 }

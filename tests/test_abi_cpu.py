@@ -89,13 +89,11 @@ def api_script(capi, lib):
     record("add out of range", lambda: out_of_range.add_gemm(t[0], t[1], t[2], capi.RoleId(40), t[3], t[4]))
     record("ops(out of range)", lambda: capi.Ops(out_of_range))
 
-    # A grouped GEMM with TensorList outputs has no engine on either side.
-    grouped = capi.Pattern(lib)
-    g = [grouped.add_grouped_tensor() for _ in range(2)]
-    lists = [grouped.add_tensor_list() for _ in range(2)]
-    alpha, beta = grouped.add_tensor(), grouped.add_tensor()
-    record("add grouped", lambda: grouped.add_gemm(g[0], g[1], lists[0], lists[1], alpha, beta, kind="GroupedABGemm"))
-    record("ops(grouped: no engine)", lambda: capi.Ops(grouped))
+    # Two Gemm nodes chained through one matrix: a graph with no engine on either side.
+    chained = capi.Pattern(lib)
+    n = [chained.add_tensor() for _ in range(10)]
+    record("add chained", lambda: (chained.add_gemm(n[0], n[1], n[2], n[3], n[4], n[5]), chained.add_gemm(n[3], n[6], n[7], n[8], n[4], n[5])))
+    record("ops(chained: no engine)", lambda: capi.Ops(chained))
 
     for order in (("a", "b", "c", "alpha", "beta", "d"), ("d", "c", "b", "a", "beta", "alpha")):
         binding = capi.GemmBinding(order=order, lib=lib)
@@ -134,7 +132,7 @@ def test_device_free_api_statuses(capi):
     assert trace["ops(no operation, dangling operands)"] == unsupported
     assert trace["add duplicate input"] == ok and trace["ops(duplicate input)"] == invalid
     assert trace["add out of range"] == ok and trace["ops(out of range)"] == invalid
-    assert trace["add grouped"] == ok and trace["ops(grouped: no engine)"] == unsupported
+    assert trace["add chained"] == ok and trace["ops(chained: no engine)"] == unsupported
     assert trace["set a"] == ok and trace["set scalar"] == ok and trace["set gemm"] == ok
     for step in ("set role out of range", "set negative dim", "set strides and index type", "set no layout",
                  "set null scalar", "set bad numeric type", "set gemm invalid type", "set gemm COUNT",
@@ -153,23 +151,25 @@ def test_same_statuses_as_the_reference_build(capi, reference_capi):
         assert capi.last_status(lib) == capi.STATUS_INVALID_ARGUMENT
 
 
-def test_grouped_abcd_gemm_has_an_engine_here(capi, reference_capi):
-    """The one place where this library answers differently from the reference on purpose: the
-    GroupedABCDGemm graph (declared by the reference's public header, without an engine there) matches."""
-    def ops_status(lib):
+def test_grouped_gemms_have_engines_here(capi, reference_capi):
+    """The one place where this library answers differently from the reference on purpose: the three
+    grouped GEMM graphs (declared by the reference's public header, without engines there) match."""
+    def ops_status(lib, kind):
         pattern = capi.Pattern(lib)
-        g = [pattern.add_grouped_tensor() for _ in range(4)]
+        lists = capi.GroupedGemmBinding.LIST_ROLES[kind]
+        roles = {name: (pattern.add_tensor_list() if name in lists else pattern.add_grouped_tensor()) for name in "abcd"}
         alpha, beta = pattern.add_tensor(), pattern.add_tensor()
-        pattern.add_gemm(g[0], g[1], g[2], g[3], alpha, beta, kind="GroupedABCDGemm")
+        pattern.add_gemm(roles["a"], roles["b"], roles["c"], roles["d"], alpha, beta, kind=kind)
         try:
             capi.Ops(pattern)
             return capi.STATUS_SUCCESS
         except capi.FTrainError as error:
             return error.status
 
-    assert ops_status(capi.lib) == capi.STATUS_SUCCESS
-    if reference_capi is not None:
-        assert ops_status(reference_capi) == capi.STATUS_UNSUPPORTED
+    for kind in ("GroupedABCDGemm", "GroupedBCDGemm", "GroupedABGemm"):
+        assert ops_status(capi.lib, kind) == capi.STATUS_SUCCESS, kind
+        if reference_capi is not None:
+            assert ops_status(reference_capi, kind) == capi.STATUS_UNSUPPORTED, kind
 
 
 def test_plan_creation_without_a_device_fails_loudly(capi):

@@ -154,3 +154,62 @@ def test_description_errors(capi, binding):
     with pytest.raises(capi.FTrainError) as info:  # another number of groups
         binding.make_plan(good, operand(flat, [8], [4]), operand(flat, [4, 4], [4, 4]), operand(flat, [4, 4], [4, 4]))
     assert info.value.status == capi.STATUS_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("kind", ["GroupedBCDGemm", "GroupedABGemm"])
+def test_tensor_list_variants(capi, oracle, kind):
+    """GroupedBCDGemm (a is a TensorList: every group's A is a tensor of its own) and GroupedABGemm (c and d are
+    TensorLists: every group's result goes to its own tensor; here the last group has no addend at all)."""
+    if not torch.cuda.is_available():
+        pytest.fail("the GPU tests need a CUDA device")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.manual_seed(89)
+    shapes = [(200, 512, 384), (0, 512, 384), (129, 256, 196), (33, 1024, 260)]
+    a_list = [torch.randn(m, k, device="cuda") for m, k, n in shapes]
+    b_list = [torch.randn(k, n, device="cuda") for m, k, n in shapes]
+    c_list = [torch.randn(m, n, device="cuda") for m, k, n in shapes]
+    d_list = [torch.full((m, n), float("nan"), device="cuda") for m, k, n in shapes]
+    alpha, beta = -1.25, 0.5
+    as_list = lambda tensors, drop_last=False: [(0 if drop_last and i == len(tensors) - 1 else t.data_ptr(), tuple(t.shape), None)  # noqa: E731
+                                                for i, t in enumerate(tensors)]
+    b_flat, b_rows, b_cols = packed(b_list)
+    binding = capi.GroupedGemmBinding(kind=kind)
+    if kind == "GroupedBCDGemm":
+        c_flat, d_rows, d_cols = packed(c_list)
+        d_flat = torch.full_like(c_flat, float("nan"))
+        plan = binding.make_plan(as_list(a_list), operand(b_flat, b_rows, b_cols), operand(c_flat, d_rows, d_cols),
+                                 operand(d_flat, d_rows, d_cols), alpha, beta)
+        expected_c = c_list
+    else:
+        a_flat, a_rows, a_cols = packed(a_list)
+        plan = binding.make_plan(operand(a_flat, a_rows, a_cols), operand(b_flat, b_rows, b_cols), as_list(c_list, drop_last=True),
+                                 as_list(d_list), alpha, beta)
+        expected_c = c_list[:-1] + [None]
+    names = plan.primitive_names()
+    assert names == ["GroupedFp32Gemm3xTf32", "GroupedFp32Gemm"], names
+    for index, name in enumerate(names):
+        if kind == "GroupedBCDGemm":
+            d_flat.fill_(float("nan"))
+        else:
+            for d in d_list:
+                d.fill_(float("nan"))
+        run(capi, plan, index)
+        results = d_flat if kind == "GroupedBCDGemm" else torch.cat([d.reshape(-1) for d in d_list])
+        at = 0
+        for g, (m, k, n) in enumerate(shapes):
+            if m * n == 0:
+                continue
+            d = results[at:at + m * n].reshape(m, n)
+            at += m * n
+            c = expected_c[g]
+            exact = alpha * (a_list[g].double() @ b_list[g].double()) + (beta * c.double() if c is not None else 0.0)
+            plain = oracle.torch_reference(a_list[g], b_list[g], c, alpha, beta if c is not None else 0.0)
+            ours = oracle.scaled_error(d, exact, a_list[g] * abs(alpha), b_list[g], c, beta)
+            other = oracle.scaled_error(plain, exact, a_list[g] * abs(alpha), b_list[g], c, beta)
+            assert torch.isfinite(d).all(), f"{kind} {name}: group {g} has non-finite output"
+            if name == "GroupedFp32Gemm" and k > 300:
+                slack = 2e-5 * max(1.0, (k / 257.0) ** 0.5)
+                scale = (a_list[g].double().abs() @ b_list[g].double().abs()) * abs(alpha) + (abs(beta) * c.double().abs() if c is not None else 0.0)
+                assert ((d.double() - exact).abs() <= slack * (1.0 + scale)).all(), f"{kind} {name}: group {g}"
+            else:
+                assert ours <= 2.0 * max(other, ERROR_FLOOR), f"{kind} {name}: group {g} scaled error {ours:.3e} vs {other:.3e}"
