@@ -665,6 +665,8 @@ def k_split_records(torch, capi, world, rank, device, steps: int, peaks) -> dict
     torch.cuda.synchronize()
     record["reduce_scatter"] = {"tflops": flops / (step_ms * 1e-3) / 1e12, "ms_per_step": step_ms, "local_gemm_ms": local_ms,
                                 "reduce_scatter_ms": collective_ms, "collective_share": collective_ms / step_ms,
+                                "timed": "whole step, local GEMM alone and reduce_scatter_tensor alone, each in its own event-timed loop "
+                                         "(maximum over ranks); the loops run one after another, so clocks under the power cap differ a little",
                                 "frac_of_burst_tensor_peak_per_gpu": flops / (step_ms * 1e-3) / 1e12 / world / (peaks["bf16_tflops"] / 6.0),
                                 **parity(out)}
     try:
