@@ -68,9 +68,10 @@ constexpr int kRawBBytes = kBoxes * kBoxBytes;  // 16 KiB
 // Shared memory per padded row count: raw slots (B tile + A tile) | stages (B_hi, B_lo, A_hi, A_lo) |
 // received sums [sender][row][column share] | barriers. Four raw slots cover the TMA latency (about
 // 2 us under load, four K-block periods); the converted stages take what is left of the 227 KiB:
-// three, or two for the 64-row form, whose stages are 48 KiB.
+// three, or two for the 64-row form, whose stages are 48 KiB. The 16-row form has room for six raw
+// slots, worth 3 % (two slots instead of four cost 25 %).
 __host__ __device__ constexpr int aBytes(int rows) { return rows * kBlockK * 4; }
-__host__ __device__ constexpr int rawSlots(int rows) { return 4; }
+__host__ __device__ constexpr int rawSlots(int rows) { return rows <= 16 ? 6 : 4; }
 __host__ __device__ constexpr int stages(int rows) { return rows <= 32 ? 3 : 2; }
 __host__ __device__ constexpr int rawSlotBytes(int rows) { return kRawBBytes + aBytes(rows); }
 __host__ __device__ constexpr int stageBytes(int rows) { return 2 * kRawBBytes + 2 * aBytes(rows); }
@@ -80,7 +81,7 @@ __host__ __device__ constexpr int receiveBytes(int rows) { return rows * kStripC
 __host__ __device__ constexpr int barrierOffset(int rows) { return receiveOffset(rows) + receiveBytes(rows); }
 __host__ __device__ constexpr int smemBytes(int rows) { return barrierOffset(rows) + 256 + 1024; }
 static_assert(smemBytes(16) <= 232448 && smemBytes(32) <= 232448 && smemBytes(64) <= 232448, "shared memory budget");
-constexpr int kMaxRawSlots = 4;
+constexpr int kMaxRawSlots = 6;
 
 constexpr int kThreads        = 512;
 constexpr int kProducerWarp   = 0;
