@@ -95,6 +95,10 @@ constexpr int kBarrierOffset = kStageOffset + kStages * kStageBytes;
 constexpr int kSmemBytes     = kBarrierOffset + 256 + 1024;  // + barriers + alignment slack
 
 constexpr int kThreads         = 640;  // 20 warps
+constexpr int kRegsLight       = 72;   // producer, issuer, converters (warpgroups 0, 1, 4)
+constexpr int kRegsDrain       = 128;  // drain / epilogue (warpgroups 2, 3)
+static_assert(kStages == 2, "the issuer's descriptor table is indexed by s == 0");
+static_assert(384 * kRegsLight + 256 * kRegsDrain <= 96 * kThreads, "the CTA's register pool is what it was launched with");
 constexpr int kProducerWarp    = 0;
 constexpr int kMmaWarp         = 1;
 constexpr int kFirstAConverter = 4;   // warps 4..7 convert A (warp % 4 = tensor-memory lane quadrant)
@@ -174,202 +178,11 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // (it % 2). The producer and MMA warps keep all 32 lanes in their loops (so
     // that the warp is converged at the block-wide barrier at the end); lane 0
     // alone issues copies, MMAs and commits.
-    if (warp == kProducerWarp) {
-        // ------------------------------------------------------------ producer
-        std::uint32_t it = 0;
-        bool ok          = true;
-        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const ItemView view   = fetchItem<kClustered, kGrouped>(p, item, kTileM);
-            const WorkItem& w     = view.w;
-            const void* const at_a = kGrouped ? static_cast<const void*>(&view.group->map_a) : static_cast<const void*>(&map_a);
-            const void* const at_b = kGrouped ? static_cast<const void*>(&view.group->map_b) : static_cast<const void*>(&map_b);
-            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const std::uint32_t r      = it % kRawSlots;
-                const std::uint32_t use    = it / kRawSlots;
-                unsigned char* slot        = smem + r * kRawSlotBytes;
-                const std::int32_t k_coord = static_cast<std::int32_t>(w.k_begin + kb * kTileK);
-                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->raw_empty[r], (use & 1) ^ 1, abort_flag));
-                if (!ok) { break; }
-                if (lane == 0) {
-                    mbarrierArriveExpectTx(&bars->raw_full[r], kRawSlotBytes);
-                    if (p.a_m_contiguous != 0) {
-                        tmaLoad2d(slot, at_a, &bars->raw_full[r], static_cast<std::int32_t>(w.tile_m), k_coord);
-                    } else {
-                        tmaLoad2d(slot, at_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
-                    }
-                    if (p.b_k_contiguous != 0) {
-                        // One box: 192 rows (n) of 32 K values, already in the MMA's K-major layout.
-                        tmaLoad2d(slot + kRawABytes, at_b, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_n));
-                    } else {
-                        for (int q = 0; q < kBoxes; ++q) {
-                            tmaLoad2d(slot + kRawABytes + q * kBoxBytes, at_b, &bars->raw_full[r],
-                                      static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
-                        }
-                    }
-                }
-                __syncwarp();
-            }
-        }
-        if (!ok) { *abort_flag = 1; }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------ MMA issuer
-        // Row-major B stays N-contiguous in shared memory (MN-major operand); a B
-        // given contiguous along K is a K-major operand.
-        const std::uint32_t kInstruction =
-            umaInstructionTf32(kTileM, kTileN) | (p.b_k_contiguous != 0 ? 0U : kUmaBMnMajor);
-        std::uint32_t it     = 0;
-        std::uint32_t chunks = 0;  // chunks started so far, over all items
-        bool ok              = true;
-        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const ItemView view = fetchItem<kClustered, kGrouped>(p, item, kTileM);
-            const WorkItem& w   = view.w;
-            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const bool chunk_start = kb % view.chunk_k_blocks == 0;
-                if (chunk_start) {
-                    // The drain warps must have emptied the chunk accumulator.
-                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag));
-                    if (!ok) { break; }
-                    ++chunks;
-                }
-                const std::uint32_t s   = it % kStages;
-                const std::uint32_t use = it / kStages;
-                ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->conv_done[s], use & 1, abort_flag));
-                if (!ok) { break; }
-                tcgen05FenceAfterSync();
-                if (lane == 0) {
-                    const std::uint32_t stage = smemAddress(smem + kStageOffset + s * kStageBytes);
-                    const bool k_major        = p.b_k_contiguous != 0;
-                    const std::uint64_t b_hi  = k_major ? umaDescriptorK128(stage + kBHiOffset)
-                                                        : umaDescriptorMn128Base32(stage + kBHiOffset, kBoxBytes, 512);
-                    const std::uint64_t b_lo  = k_major ? umaDescriptorK128(stage + kBLoOffset)
-                                                        : umaDescriptorMn128Base32(stage + kBLoOffset, kBoxBytes, 512);
-                    // Eight k further: 32 bytes within a K-major row, two 512-byte atoms in an MN-major tile.
-                    const std::uint64_t k_step = k_major ? 2 : 64;
-                    const std::uint32_t a_hi  = tmem_base + kAColumn + s * 64;
-                    const std::uint32_t a_lo  = a_hi + 32;
-#pragma unroll
-                    for (int step = 0; step < kTileK / 8; ++step) {
-                        // 8 TF32 elements further along K: 8 columns of tensor
-                        // memory for A, `k_step` descriptor units (of 16 bytes) for B.
-                        const std::uint64_t advance = static_cast<std::uint64_t>(step) * k_step;
-                        const std::uint32_t fresh   = (chunk_start && step == 0) ? 0U : 1U;
-                        umaTf32TmemA(tmem_base, a_lo + step * 8, b_hi + advance, kInstruction, fresh);
-                        umaTf32TmemA(tmem_base, a_hi + step * 8, b_lo + advance, kInstruction, 1U);
-                        umaTf32TmemA(tmem_base, a_hi + step * 8, b_hi + advance, kInstruction, 1U);
-                    }
-                    umaCommit(&bars->mma_done[s]);
-                    const bool chunk_end = (kb + 1) % view.chunk_k_blocks == 0 || kb + 1 == w.k_blocks;
-                    if (chunk_end) { umaCommit(&bars->acc_full); }
-                }
-                __syncwarp();
-            }
-        }
-        if (!ok) {
-            *abort_flag = 1;
-            // Let MMAs already issued finish before tensor memory is freed.
-            if (lane == 0) {
-                umaCommit(&bars->flush);
-                int never = 0;
-                mbarrierWait(&bars->flush, 0, &never);
-            }
-            __syncwarp();
-        }
-    } else if (warp < kFirstEpilogue || warp >= kFirstLateB) {
-        // ------------------------------------------------------------ converters
-        const bool converts_a = warp >= kFirstAConverter && warp < kFirstEpilogue;
-        const int box_index   = warp < kFirstAConverter ? warp - 2 : warp - kFirstLateB + 2;  // B box of a B converter
-        const int a_row       = 32 * (warp & 3) + lane;   // row of A = TMEM lane (warp % 4 selects the lane quadrant)
-        std::uint32_t it = 0;
-        bool ok          = true;
-        for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-            const WorkItem w = fetchItem<kClustered, kGrouped>(p, item, kTileM).w;
-            for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
-                const std::uint32_t r      = it % kRawSlots;
-                const std::uint32_t s      = it % kStages;
-                const unsigned char* slot  = smem + r * kRawSlotBytes;
-                unsigned char* stage       = smem + kStageOffset + s * kStageBytes;
-                ok = mbarrierWait(&bars->raw_full[r], (it / kRawSlots) & 1, abort_flag);
-                if (!ok) { break; }
-                // The stage (B tiles and A columns) is free once the MMAs of its
-                // previous use have completed.
-                ok = mbarrierWait(&bars->mma_done[s], ((it / kStages) & 1) ^ 1, abort_flag);
-                if (!ok) { break; }
-                tcgen05FenceAfterSync();
-                if (converts_a) {
-                    // One row of A per thread: 8 chunks of 4 floats, un-swizzled by
-                    // the row index, split, and stored to this stage's A columns.
-                    const unsigned char* row   = slot + a_row * 128;
-                    const std::uint32_t a_tmem = tmem_base + (static_cast<std::uint32_t>(32 * (warp & 3)) << 16) +
-                                                 kAColumn + s * 64;
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        float hi[16];
-                        float lo[16];
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int chunk = half * 4 + c;
-                            float values[4];
-                            if (p.a_m_contiguous != 0) {
-                                // Raw tile is [32 k][128 m], linear: a column per thread,
-                                // consecutive lanes read consecutive words.
-                                const float* column = reinterpret_cast<const float*>(slot) + a_row;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) { values[j] = column[(chunk * 4 + j) * kTileM]; }
-                            } else {
-                                const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
-                                values[0] = raw.x;
-                                values[1] = raw.y;
-                                values[2] = raw.z;
-                                values[3] = raw.w;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                std::uint32_t hi_bits, lo_bits;
-                                splitTf32(values[j], hi_bits, lo_bits);
-                                hi[c * 4 + j] = __uint_as_float(hi_bits);
-                                lo[c * 4 + j] = __uint_as_float(lo_bits);
-                            }
-                        }
-                        tmemStore16NoWait(a_tmem + half * 16, hi);
-                        tmemStore16NoWait(a_tmem + 32 + half * 16, lo);
-                    }
-                    tmemStoreWait();
-                } else {
-                    // B arrives in the layout the MMA reads it in -- six 32 (n) x 32 (k)
-                    // boxes of an MN-major operand for a row-major B, 192 rows (n) of a
-                    // K-major operand for a B contiguous along K, both with the
-                    // 128-byte swizzle -- so it is split element by element, same offset
-                    // in the raw tile and in B_hi / B_lo. A warp takes 4 KiB, 128 bits
-                    // per lane and step, consecutive lanes at consecutive addresses.
-                    const int offset          = box_index * kBoxBytes;
-                    const unsigned char* rows = slot + kRawABytes + offset;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int at     = c * 512 + lane * 16;
-                        const float4 raw = *reinterpret_cast<const float4*>(rows + at);
-                        uint4 hi, lo;
-                        splitTf32(raw.x, hi.x, lo.x);
-                        splitTf32(raw.y, hi.y, lo.y);
-                        splitTf32(raw.z, hi.z, lo.z);
-                        splitTf32(raw.w, hi.w, lo.w);
-                        *reinterpret_cast<uint4*>(stage + kBHiOffset + offset + at) = hi;
-                        *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
-                    }
-                }
-                // Publish: shared-memory writes to the async proxy, tensor-memory
-                // stores (already waited for) to the MMA issuer. The same proxy fence
-                // orders this warp's reads of the raw slot before its refill by TMA.
-                fenceProxyAsync();
-                tcgen05FenceBeforeSync();
-                __syncwarp();
-                if (lane == 0) {
-                    mbarrierArrive(&bars->raw_empty[r]);
-                    mbarrierArrive(&bars->conv_done[s]);
-                }
-            }
-        }
-        if (!ok) { *abort_flag = 1; }
-    } else if (warp >= kFirstEpilogue) {
+    // The drain warps keep 96 accumulator values at a time in registers; they take the registers the
+    // other roles do not need (setmaxnreg acts on warpgroups: 0 and 1 producer / issuer / converters,
+    // 2 and 3 drain, 4 converters).
+    if (warp >= kFirstEpilogue && warp < kFirstLateB) {
+        registersGrow<kRegsDrain>();
         // ------------------------------------------------------------ drain / epilogue
         const int e                   = warp - kFirstEpilogue;  // 0..7
         const std::uint32_t lane_base = static_cast<std::uint32_t>(32 * (e & 3));
@@ -407,34 +220,247 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tcgen05FenceAfterSync();
                 const bool first = chunk == 0;
                 const bool last  = chunk + 1 == num_chunks;
-                // Piece by piece (16 columns): fold in the running sum, then
-                // either write the result out (last chunk) or store the new
-                // running sum. The chunk accumulator is released as soon as
-                // its last piece has been read.
+                // The chunk accumulator goes to registers in one round trip and is handed back to the
+                // MMA issuer at once; the running sum is folded in afterwards, piece by piece (16
+                // columns), while the tensor core is already filling the accumulator again: either
+                // the result is written out (last chunk) or the new running sum stored.
+                float chunk_sum[kHalfColumns];
+                tmemLoad96(tmem_row + col_half, chunk_sum);
+                tcgen05FenceBeforeSync();
+                __syncwarp();
+                if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
 #pragma unroll
                 for (int piece = 0; piece < kPieces; ++piece) {
                     float sum[16];
-                    tmemLoad16(tmem_row + col_half + piece * 16, sum);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { sum[j] = chunk_sum[piece * 16 + j]; }
                     if (!first) {
                         float running[16];
                         tmemLoad16(tmem_row + kRunningColumn + col_half + piece * 16, running);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) { sum[j] += running[j]; }
                     }
-                    if (piece == kPieces - 1) {
-                        tcgen05FenceBeforeSync();
-                        __syncwarp();
-                        if (lane == 0) { mbarrierArrive(&bars->acc_empty); }
-                    }
                     if (last && !kClustered) {
                         writeRowSegment(out, w, row, w.tile_n + col_half + piece * 16, sum, vector_ok);
                     } else {
-                        tmemStore16(tmem_row + kRunningColumn + col_half + piece * 16, sum);
+                        tmemStore16NoWait(tmem_row + kRunningColumn + col_half + piece * 16, sum);
                     }
                 }
+                tmemStoreWait();
             }
         }
         if (!ok) { *abort_flag = 1; }
+    } else {
+        registersShrink<kRegsLight>();
+        if (warp == kProducerWarp) {
+            // ------------------------------------------------------------ producer
+            std::uint32_t it = 0;
+            bool ok          = true;
+            for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const ItemView view   = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+                const WorkItem& w     = view.w;
+                const void* const at_a = kGrouped ? static_cast<const void*>(&view.group->map_a) : static_cast<const void*>(&map_a);
+                const void* const at_b = kGrouped ? static_cast<const void*>(&view.group->map_b) : static_cast<const void*>(&map_b);
+                for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
+                    const std::uint32_t r      = it % kRawSlots;
+                    const std::uint32_t use    = it / kRawSlots;
+                    unsigned char* slot        = smem + r * kRawSlotBytes;
+                    const std::int32_t k_coord = static_cast<std::int32_t>(w.k_begin + kb * kTileK);
+                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->raw_empty[r], (use & 1) ^ 1, abort_flag));
+                    if (!ok) { break; }
+                    if (lane == 0) {
+                        mbarrierArriveExpectTx(&bars->raw_full[r], kRawSlotBytes);
+                        if (p.a_m_contiguous != 0) {
+                            tmaLoad2d(slot, at_a, &bars->raw_full[r], static_cast<std::int32_t>(w.tile_m), k_coord);
+                        } else {
+                            tmaLoad2d(slot, at_a, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_m));
+                        }
+                        if (p.b_k_contiguous != 0) {
+                            // One box: 192 rows (n) of 32 K values, already in the MMA's K-major layout.
+                            tmaLoad2d(slot + kRawABytes, at_b, &bars->raw_full[r], k_coord, static_cast<std::int32_t>(w.tile_n));
+                        } else {
+                            for (int q = 0; q < kBoxes; ++q) {
+                                tmaLoad2d(slot + kRawABytes + q * kBoxBytes, at_b, &bars->raw_full[r],
+                                          static_cast<std::int32_t>(w.tile_n + q * 32), k_coord);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok) { *abort_flag = 1; }
+        } else if (warp == kMmaWarp) {
+            // ------------------------------------------------------------ MMA issuer
+            // Row-major B stays N-contiguous in shared memory (MN-major operand); a B
+            // given contiguous along K is a K-major operand.
+            const std::uint32_t kInstruction =
+                umaInstructionTf32(kTileM, kTileN) | (p.b_k_contiguous != 0 ? 0U : kUmaBMnMajor);
+            // The issuing thread's own time per K block is what the tensor core waits for, so its loop
+            // carries counters instead of divisions and takes its operand descriptors from a table
+            // made once (they depend on the stage alone).
+            const bool k_major = p.b_k_contiguous != 0;
+            // Eight k further: 32 bytes within a K-major row, two 512-byte atoms in an MN-major tile.
+            const std::uint64_t k_step = k_major ? 2 : 64;
+            std::uint64_t b_hi_of[kStages];
+            std::uint64_t b_lo_of[kStages];
+#pragma unroll
+            for (int stage_index = 0; stage_index < kStages; ++stage_index) {
+                const std::uint32_t stage = smemAddress(smem + kStageOffset + stage_index * kStageBytes);
+                b_hi_of[stage_index] = k_major ? umaDescriptorK128(stage + kBHiOffset) : umaDescriptorMn128Base32(stage + kBHiOffset, kBoxBytes, 512);
+                b_lo_of[stage_index] = k_major ? umaDescriptorK128(stage + kBLoOffset) : umaDescriptorMn128Base32(stage + kBLoOffset, kBoxBytes, 512);
+            }
+            std::uint32_t s            = 0;  // stage of this K block and the parity of its barrier
+            std::uint32_t stage_parity = 0;
+            std::uint32_t chunks       = 0;  // chunks started so far, over all items
+            bool ok                    = true;
+            for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const ItemView view = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+                const WorkItem& w   = view.w;
+                std::uint32_t in_chunk = 0;  // K blocks accumulated into the current chunk
+                for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb) {
+                    const bool chunk_start = in_chunk == 0;
+                    if (chunk_start) {
+                        // The drain warps must have emptied the chunk accumulator.
+                        ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag));
+                        if (!ok) { break; }
+                        ++chunks;
+                    }
+                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->conv_done[s], stage_parity, abort_flag));
+                    if (!ok) { break; }
+                    tcgen05FenceAfterSync();
+                    const bool chunk_end = in_chunk + 1 == view.chunk_k_blocks || kb + 1 == w.k_blocks;
+                    if (lane == 0) {
+                        const std::uint64_t b_hi = s == 0 ? b_hi_of[0] : b_hi_of[kStages - 1];
+                        const std::uint64_t b_lo = s == 0 ? b_lo_of[0] : b_lo_of[kStages - 1];
+                        const std::uint32_t a_hi = tmem_base + kAColumn + s * 64;
+                        const std::uint32_t a_lo = a_hi + 32;
+#pragma unroll
+                        for (int step = 0; step < kTileK / 8; ++step) {
+                            // 8 TF32 elements further along K: 8 columns of tensor
+                            // memory for A, `k_step` descriptor units (of 16 bytes) for B.
+                            const std::uint64_t advance = static_cast<std::uint64_t>(step) * k_step;
+                            const std::uint32_t fresh   = (chunk_start && step == 0) ? 0U : 1U;
+                            umaTf32TmemA(tmem_base, a_lo + step * 8, b_hi + advance, kInstruction, fresh);
+                            umaTf32TmemA(tmem_base, a_hi + step * 8, b_lo + advance, kInstruction, 1U);
+                            umaTf32TmemA(tmem_base, a_hi + step * 8, b_hi + advance, kInstruction, 1U);
+                        }
+                        umaCommit(&bars->mma_done[s]);
+                        if (chunk_end) { umaCommit(&bars->acc_full); }
+                    }
+                    in_chunk = chunk_end ? 0 : in_chunk + 1;
+                    if (++s == kStages) {
+                        s = 0;
+                        stage_parity ^= 1;
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                // Let MMAs already issued finish before tensor memory is freed.
+                if (lane == 0) {
+                    umaCommit(&bars->flush);
+                    int never = 0;
+                    mbarrierWait(&bars->flush, 0, &never);
+                }
+                __syncwarp();
+            }
+        } else if (warp < kFirstEpilogue || warp >= kFirstLateB) {
+            // ------------------------------------------------------------ converters
+            const bool converts_a = warp >= kFirstAConverter && warp < kFirstEpilogue;
+            const int box_index   = warp < kFirstAConverter ? warp - 2 : warp - kFirstLateB + 2;  // B box of a B converter
+            const int a_row       = 32 * (warp & 3) + lane;   // row of A = TMEM lane (warp % 4 selects the lane quadrant)
+            std::uint32_t it = 0;
+            bool ok          = true;
+            for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const WorkItem w = fetchItem<kClustered, kGrouped>(p, item, kTileM).w;
+                for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb, ++it) {
+                    const std::uint32_t r      = it % kRawSlots;
+                    const std::uint32_t s      = it % kStages;
+                    const unsigned char* slot  = smem + r * kRawSlotBytes;
+                    unsigned char* stage       = smem + kStageOffset + s * kStageBytes;
+                    ok = mbarrierWait(&bars->raw_full[r], (it / kRawSlots) & 1, abort_flag);
+                    if (!ok) { break; }
+                    // The stage (B tiles and A columns) is free once the MMAs of its
+                    // previous use have completed.
+                    ok = mbarrierWait(&bars->mma_done[s], ((it / kStages) & 1) ^ 1, abort_flag);
+                    if (!ok) { break; }
+                    tcgen05FenceAfterSync();
+                    if (converts_a) {
+                        // One row of A per thread: 8 chunks of 4 floats, un-swizzled by
+                        // the row index, split, and stored to this stage's A columns.
+                        const unsigned char* row   = slot + a_row * 128;
+                        const std::uint32_t a_tmem = tmem_base + (static_cast<std::uint32_t>(32 * (warp & 3)) << 16) +
+                                                     kAColumn + s * 64;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            float hi[16];
+                            float lo[16];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const int chunk = half * 4 + c;
+                                float values[4];
+                                if (p.a_m_contiguous != 0) {
+                                    // Raw tile is [32 k][128 m], linear: a column per thread,
+                                    // consecutive lanes read consecutive words.
+                                    const float* column = reinterpret_cast<const float*>(slot) + a_row;
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) { values[j] = column[(chunk * 4 + j) * kTileM]; }
+                                } else {
+                                    const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
+                                    values[0] = raw.x;
+                                    values[1] = raw.y;
+                                    values[2] = raw.z;
+                                    values[3] = raw.w;
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    std::uint32_t hi_bits, lo_bits;
+                                    splitTf32(values[j], hi_bits, lo_bits);
+                                    hi[c * 4 + j] = __uint_as_float(hi_bits);
+                                    lo[c * 4 + j] = __uint_as_float(lo_bits);
+                                }
+                            }
+                            tmemStore16NoWait(a_tmem + half * 16, hi);
+                            tmemStore16NoWait(a_tmem + 32 + half * 16, lo);
+                        }
+                        tmemStoreWait();
+                    } else {
+                        // B arrives in the layout the MMA reads it in -- six 32 (n) x 32 (k)
+                        // boxes of an MN-major operand for a row-major B, 192 rows (n) of a
+                        // K-major operand for a B contiguous along K, both with the
+                        // 128-byte swizzle -- so it is split element by element, same offset
+                        // in the raw tile and in B_hi / B_lo. A warp takes 4 KiB, 128 bits
+                        // per lane and step, consecutive lanes at consecutive addresses.
+                        const int offset          = box_index * kBoxBytes;
+                        const unsigned char* rows = slot + kRawABytes + offset;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const int at     = c * 512 + lane * 16;
+                            const float4 raw = *reinterpret_cast<const float4*>(rows + at);
+                            uint4 hi, lo;
+                            splitTf32(raw.x, hi.x, lo.x);
+                            splitTf32(raw.y, hi.y, lo.y);
+                            splitTf32(raw.z, hi.z, lo.z);
+                            splitTf32(raw.w, hi.w, lo.w);
+                            *reinterpret_cast<uint4*>(stage + kBHiOffset + offset + at) = hi;
+                            *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
+                        }
+                    }
+                    // Publish: shared-memory writes to the async proxy, tensor-memory
+                    // stores (already waited for) to the MMA issuer. The same proxy fence
+                    // orders this warp's reads of the raw slot before its refill by TMA.
+                    fenceProxyAsync();
+                    tcgen05FenceBeforeSync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbarrierArrive(&bars->raw_empty[r]);
+                        mbarrierArrive(&bars->conv_done[s]);
+                    }
+                }
+            }
+            if (!ok) { *abort_flag = 1; }
+        }
     }
 
     __syncthreads();
