@@ -386,40 +386,43 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     ok = mbarrierWait(&bars->mma_done[s], ((it / kStages) & 1) ^ 1, abort_flag);
                     if (!ok) { break; }
                     tcgen05FenceAfterSync();
+                    // Both kinds of converter first bring ALL their raw values into registers and only
+                    // then split and store: a store in between (shared memory, or the tensor-memory
+                    // store with its memory clobber) would pin every later load behind it, and the
+                    // conversion would be eight load-split-store round trips one after the other.
                     if (converts_a) {
                         // One row of A per thread: 8 chunks of 4 floats, un-swizzled by
                         // the row index, split, and stored to this stage's A columns.
                         const unsigned char* row   = slot + a_row * 128;
                         const std::uint32_t a_tmem = tmem_base + (static_cast<std::uint32_t>(32 * (warp & 3)) << 16) +
                                                      kAColumn + s * 64;
+                        float values[kTileK];
+                        if (p.a_m_contiguous != 0) {
+                            // Raw tile is [32 k][128 m], linear: a column per thread,
+                            // consecutive lanes read consecutive words.
+                            const float* column = reinterpret_cast<const float*>(slot) + a_row;
+#pragma unroll
+                            for (int j = 0; j < kTileK; ++j) { values[j] = column[j * kTileM]; }
+                        } else {
+#pragma unroll
+                            for (int chunk = 0; chunk < kTileK / 4; ++chunk) {
+                                const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
+                                values[chunk * 4 + 0] = raw.x;
+                                values[chunk * 4 + 1] = raw.y;
+                                values[chunk * 4 + 2] = raw.z;
+                                values[chunk * 4 + 3] = raw.w;
+                            }
+                        }
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
                             float hi[16];
                             float lo[16];
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const int chunk = half * 4 + c;
-                                float values[4];
-                                if (p.a_m_contiguous != 0) {
-                                    // Raw tile is [32 k][128 m], linear: a column per thread,
-                                    // consecutive lanes read consecutive words.
-                                    const float* column = reinterpret_cast<const float*>(slot) + a_row;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) { values[j] = column[(chunk * 4 + j) * kTileM]; }
-                                } else {
-                                    const float4 raw = *reinterpret_cast<const float4*>(row + ((chunk ^ (a_row & 7)) << 4));
-                                    values[0] = raw.x;
-                                    values[1] = raw.y;
-                                    values[2] = raw.z;
-                                    values[3] = raw.w;
-                                }
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    std::uint32_t hi_bits, lo_bits;
-                                    splitTf32(values[j], hi_bits, lo_bits);
-                                    hi[c * 4 + j] = __uint_as_float(hi_bits);
-                                    lo[c * 4 + j] = __uint_as_float(lo_bits);
-                                }
+                            for (int j = 0; j < 16; ++j) {
+                                std::uint32_t hi_bits, lo_bits;
+                                splitTf32(values[half * 16 + j], hi_bits, lo_bits);
+                                hi[j] = __uint_as_float(hi_bits);
+                                lo[j] = __uint_as_float(lo_bits);
                             }
                             tmemStore16NoWait(a_tmem + half * 16, hi);
                             tmemStore16NoWait(a_tmem + 32 + half * 16, lo);
@@ -434,15 +437,17 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         // per lane and step, consecutive lanes at consecutive addresses.
                         const int offset          = box_index * kBoxBytes;
                         const unsigned char* rows = slot + kRawABytes + offset;
+                        float4 raw[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) { raw[c] = *reinterpret_cast<const float4*>(rows + c * 512 + lane * 16); }
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
-                            const int at     = c * 512 + lane * 16;
-                            const float4 raw = *reinterpret_cast<const float4*>(rows + at);
+                            const int at = c * 512 + lane * 16;
                             uint4 hi, lo;
-                            splitTf32(raw.x, hi.x, lo.x);
-                            splitTf32(raw.y, hi.y, lo.y);
-                            splitTf32(raw.z, hi.z, lo.z);
-                            splitTf32(raw.w, hi.w, lo.w);
+                            splitTf32(raw[c].x, hi.x, lo.x);
+                            splitTf32(raw[c].y, hi.y, lo.y);
+                            splitTf32(raw[c].z, hi.z, lo.z);
+                            splitTf32(raw[c].w, hi.w, lo.w);
                             *reinterpret_cast<uint4*>(stage + kBHiOffset + offset + at) = hi;
                             *reinterpret_cast<uint4*>(stage + kBLoOffset + offset + at) = lo;
                         }
