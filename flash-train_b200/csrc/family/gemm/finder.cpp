@@ -51,10 +51,11 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     const bool b_along_k = problem.getLayout(GemmPort::kB).row_stride == 1 && shape.n > 1;
     // The tensor few-rows kernel (B as the tensor core's 128-row operand): one CTA per 128-column
     // strip and K slice, at most eight slices. Measured against the other families on B200:
-    // it wins from 12 rows on for large B (from 17 rows whatever the size, K >= 1024), and up
+    // it wins from 9 rows on for large B -- where the exact few-rows kernel changes to its 16-row form:
+    // 22 against 27 us at 9 to 12 rows of 4096 x 4096 -- (from 17 rows whatever the size, K >= 1024), and up
     // to 64 rows, except where a narrow, deep problem leaves it too few CTAs: then the
     // split-K tensor kernel, which cuts K as finely as it likes, comes first.
-    if (shape.m >= 12 && shape.m <= 64 && shape.n >= 128 && shape.k >= 256) {
+    if (shape.m >= 9 && shape.m <= 64 && shape.n >= 128 && shape.k >= 256) {
         const std::uint64_t strips = ceilDiv(shape.n, 128);
         bool rows_first            = false;
         bool deep                  = false;  // too deep for eight K slices per strip

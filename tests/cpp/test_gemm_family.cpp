@@ -238,12 +238,13 @@ TEST(finder_regime_map) {
     };
     using Names = std::vector<std::string>;
     CHECK(first(1, 4096, 4096) == (Names{"Fp32GemmSkinny", "Fp32GemmSplitK", "Fp32Gemm"}));
-    // From 12 rows on (17 whatever the size of B) B goes through the tensor cores as their 128-row operand.
+    // From 9 rows on (17 whatever the size of B) B goes through the tensor cores as their 128-row operand.
     CHECK(first(17, 4096, 4096) == (Names{"Fp32Gemm3xTf32FewRows", "Fp32Gemm3xTf32SplitK", "Fp32GemmSkinny", "Fp32Gemm3xTf32",
                                           "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(12, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(12, 2048, 2048).front() == "Fp32GemmSkinny");
-    CHECK(first(11, 4096, 4096).front() == "Fp32GemmSkinny");
+    CHECK(first(9, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
+    CHECK(first(8, 4096, 4096).front() == "Fp32GemmSkinny");
     CHECK(first(17, 512, 4096).front() == "Fp32GemmSkinny");
     // 2 x 22 tiles on 148 SMs, K = 4096: the single launch cuts K over clusters of three.
     CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
