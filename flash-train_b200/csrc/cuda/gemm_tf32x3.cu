@@ -313,23 +313,24 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             std::uint32_t stage_parity = 0;
             std::uint32_t chunks       = 0;  // chunks started so far, over all items
             bool ok                    = true;
-            for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-                const ItemView view = fetchItem<kClustered, kGrouped>(p, item, kTileM);
-                const WorkItem& w   = view.w;
-                std::uint32_t in_chunk = 0;  // K blocks accumulated into the current chunk
-                for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb) {
-                    const bool chunk_start = in_chunk == 0;
-                    if (chunk_start) {
-                        // The drain warps must have emptied the chunk accumulator.
-                        ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag));
+            // One thread walks the loop; the other lanes of the warp wait at the end.
+            if (lane == 0) {
+                for (std::uint32_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                    const ItemView view = fetchItem<kClustered, kGrouped>(p, item, kTileM);
+                    const WorkItem& w   = view.w;
+                    std::uint32_t in_chunk = 0;  // K blocks accumulated into the current chunk
+                    for (std::uint32_t kb = 0; kb < w.k_blocks && ok; ++kb) {
+                        const bool chunk_start = in_chunk == 0;
+                        if (chunk_start) {
+                            // The drain warps must have emptied the chunk accumulator.
+                            ok = mbarrierWait(&bars->acc_empty, (chunks & 1) ^ 1, abort_flag);
+                            if (!ok) { break; }
+                            ++chunks;
+                        }
+                        ok = mbarrierWait(&bars->conv_done[s], stage_parity, abort_flag);
                         if (!ok) { break; }
-                        ++chunks;
-                    }
-                    ok = __all_sync(0xFFFFFFFFU, mbarrierWait(&bars->conv_done[s], stage_parity, abort_flag));
-                    if (!ok) { break; }
-                    tcgen05FenceAfterSync();
-                    const bool chunk_end = in_chunk + 1 == view.chunk_k_blocks || kb + 1 == w.k_blocks;
-                    if (lane == 0) {
+                        tcgen05FenceAfterSync();
+                        const bool chunk_end = in_chunk + 1 == view.chunk_k_blocks || kb + 1 == w.k_blocks;
                         const std::uint64_t b_hi = s == 0 ? b_hi_of[0] : b_hi_of[kStages - 1];
                         const std::uint64_t b_lo = s == 0 ? b_lo_of[0] : b_lo_of[kStages - 1];
                         const std::uint32_t a_hi = tmem_base + kAColumn + s * 64;
@@ -346,15 +347,15 @@ tensorGemm3xTf32(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         }
                         umaCommit(&bars->mma_done[s]);
                         if (chunk_end) { umaCommit(&bars->acc_full); }
+                        in_chunk = chunk_end ? 0 : in_chunk + 1;
+                        if (++s == kStages) {
+                            s = 0;
+                            stage_parity ^= 1;
+                        }
                     }
-                    in_chunk = chunk_end ? 0 : in_chunk + 1;
-                    if (++s == kStages) {
-                        s = 0;
-                        stage_parity ^= 1;
-                    }
-                    __syncwarp();
                 }
             }
+            ok = __all_sync(0xFFFFFFFFU, ok);
             if (!ok) {
                 *abort_flag = 1;
                 // Let MMAs already issued finish before tensor memory is freed.
