@@ -18,7 +18,8 @@
 //               view -- the raw tile is [k][m] and a thread reads its column),
 //               split it and store a_hi / a_lo into TENSOR MEMORY
 //               (tcgen05.st), from where the MMA takes its A operand. A never
-//               occupies MMA-side shared memory or its read bandwidth.
+//               occupies MMA-side shared memory or its read bandwidth. Like the
+//               B converters they load everything first and store afterwards.
 //   warps 2,3,  B converters, 4 KiB of the B tile per warp. The raw tile already has
 //   16-19       the layout the MMA reads: for a row-major B the six boxes (copied
 //               with the 32-byte-base variant of the 128-byte swizzle) are the
@@ -27,17 +28,27 @@
 //               is a K-major operand. Either way the split is element by element:
 //               128-bit reads and writes at the same offset into B_hi / B_lo,
 //               consecutive lanes at consecutive addresses.
-//   warp 1      MMA issuer (one thread): 4 K-steps x 3 products per K block,
-//               A from tensor memory, B by shared-memory descriptor (MN-major or
-//               K-major, see above), into the
+//   warp 1      MMA issuer (one thread walks the whole loop): 4 K-steps x 3
+//               products per K block, A from tensor memory, B by shared-memory
+//               descriptor (MN-major or K-major, see above), into the
 //               "chunk" accumulator (TMEM columns 0-191). A tcgen05.commit per
-//               K block releases the stage (its B tiles and its A columns).
+//               K block releases the stage (its B tiles and its A columns). An
+//               MMA issue returns when the pipe has taken the instruction, so
+//               whatever else this thread does between two K blocks is time the
+//               tensor core idles: its loop carries counters and a table of
+//               descriptors, no divisions, no warp votes.
 //   warps 8-15  drain / epilogue. Every `chunk_k_blocks` K blocks the chunk
 //               accumulator is added, in round-to-nearest FP32, to a running
 //               sum kept in TMEM columns 192-383, and the chunk restarts from
 //               zero (the interval grows with sqrt(K), see chunkKBlocks). This
 //               bounds the length of any accumulation chain inside the tensor
-//               core, whose internal FP32 additions truncate. After the last
+//               core, whose internal FP32 additions truncate. A drain warp
+//               reads its 32 lanes x 96 columns of the accumulator in one round
+//               trip and hands the accumulator back at once; the running sum is
+//               updated after that, while the next chunk is already being
+//               multiplied. The 96 values live in registers: setmaxnreg moves
+//               registers from the other roles (72 per thread) to the drain
+//               warps (128). After the last
 //               chunk the sum is scaled and written out -- or stored raw as a
 //               split-K partial, or added into the rows' owners' buffers
 //               (scatter launches) -- while the next tile's first chunk is
