@@ -99,11 +99,12 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
         const std::uint64_t tiles = ceilDiv(shape.m, 128) * ceilDiv(shape.n, 192);
         const std::uint64_t waves = ceilDiv(tiles, sm_count);
         const bool ragged         = tiles * 10 < waves * sm_count * 9;  // the waves are under 90 % full overall
-        // With few tiles the single-launch kernel cuts K over a thread-block cluster by itself. Between a
-        // quarter and half a wave of tiles (clusters of 2 or 3) and a K of at most 4096 that beats split-K
-        // with its second kernel (256 x 4096 x 4096: 60 against 68 us); deeper K or fewer tiles stay with
-        // split-K and its finer slices.
-        if (tiles * 2 <= sm_count && tiles * 4 > sm_count && shape.k >= 512 && shape.k <= 4096) {
+        // With few tiles the single-launch kernel cuts K over a thread-block cluster by itself. Under half
+        // a wave of tiles that beats split-K with its second kernel whenever K is at most 2048 (one tile
+        // of 128 x 1024 x 192: 16 against 21 us; 256 x 2048 x 2048: 25 against 27) and, up to a K of 4096,
+        // from an eighth of a wave on (128 x 4096 x 4096, 22 tiles: 35 against 41 us; 8 tiles: 31 against
+        // 27); deeper K or fewer tiles stay with split-K and its finer slices.
+        if (tiles * 2 <= sm_count && shape.k >= 512 && (shape.k <= 2048 || (shape.k <= 4096 && tiles * 8 >= sm_count))) {
             return {tensor, tensor_split, simt_split, simt};
         }
         if (ragged && shape.k >= 2048) { return {tensor_split, tensor, simt_split, simt}; }

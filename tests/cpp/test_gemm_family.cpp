@@ -248,13 +248,18 @@ TEST(finder_regime_map) {
     CHECK(first(17, 512, 4096).front() == "Fp32GemmSkinny");
     // 2 x 22 tiles on 148 SMs, K = 4096: the single launch cuts K over clusters of three.
     CHECK(first(255, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
-    // The same tiles with a deeper K, or half as many tiles: the two-launch split-K cuts finer.
+    // The same tiles with a deeper K, or under an eighth of a wave of tiles at K = 4096: the two-launch
+    // split-K cuts finer. Half as many tiles (22) still go to the single launch, and so does any
+    // number of tiles under half a wave when K is at most 2048.
     CHECK(first(255, 16384, 4096).front() == "Fp32Gemm3xTf32SplitK");
-    CHECK(first(128, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(128, 4096, 4096).front() == "Fp32Gemm3xTf32");
+    CHECK(first(128, 4096, 1536).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(128, 2048, 768).front() == "Fp32Gemm3xTf32");
+    CHECK(first(128, 3072, 1152).front() == "Fp32Gemm3xTf32SplitK");
     CHECK(first(4097, 4096, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     // From 33 rows on the tensor kernel's 128-row tile wins over the SIMT kernel.
     CHECK(first(64, 4096, 4096).front() == "Fp32Gemm3xTf32FewRows");
-    CHECK(first(65, 4096, 4096).front() == "Fp32Gemm3xTf32SplitK");
+    CHECK(first(65, 4096, 4096).front() == "Fp32Gemm3xTf32");
     // Narrow and deep: eight K slices per strip are too few CTAs.
     CHECK(first(64, 8192, 1024).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(48, 65536, 512)[1] == "Fp32Gemm3xTf32FewRows");
@@ -268,7 +273,7 @@ TEST(finder_regime_map) {
     CHECK(first(17, 1024, 1024).front() == "Fp32GemmSkinny");
     CHECK(first(17, 2048, 512).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(64, 1024, 1024).front() == "Fp32Gemm3xTf32FewRows");
-    CHECK(first(96, 1024, 1024) == (Names{"Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32", "Fp32GemmSplitK", "Fp32Gemm"}));
+    CHECK(first(96, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 4096) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm"}));
     CHECK(first(1024, 1024, 1024) == (Names{"Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32GemmSplitK", "Fp32Gemm"}));
     // Few rows but a narrow B: too few strips for the few-rows kernel.
