@@ -434,6 +434,51 @@ class PlanRunner:
         self.plan.execute(self.index, self.pointer, self.size, self.stream)
 
 
+def tf32_library_probe(torch, device, peaks):
+    """cuBLAS TF32 (torch.matmul on FP32 tensors with allow_tf32) on 8192^3: the library's own rate for ONE TF32 product,
+    best of 10 (burst) and back to back for two seconds (sustained). A yardstick beside the BF16 / 6 denominators, not a
+    code path of this library: a third of it is what three TF32 products per FP32 product could reach."""
+    n = 8192
+    x = torch.randn(n, n, device=device)
+    y = torch.randn(n, n, device=device)
+    out = torch.empty(n, n, device=device)
+    before = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        for _ in range(3):
+            torch.matmul(x, y, out=out)
+        torch.cuda.synchronize(device)
+        flops = 2.0 * n * n * n
+        best_ms = None
+        for _ in range(10):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            torch.matmul(x, y, out=out)
+            stop.record()
+            torch.cuda.synchronize(device)
+            elapsed = start.elapsed_time(stop)
+            best_ms = elapsed if best_ms is None else min(best_ms, elapsed)
+        repeats = max(10, int(2000.0 / best_ms))
+        with ClockSampler(device.index or 0) as sampler:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(repeats):
+                torch.matmul(x, y, out=out)
+            stop.record()
+            torch.cuda.synchronize(device)
+        clocks = sampler.summary()
+        sustained_ms = start.elapsed_time(stop) / repeats
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = before
+    burst, sustained = flops / (best_ms * 1e-3) / 1e12, flops / (sustained_ms * 1e-3) / 1e12
+    return {"shape": [n, n, n], "burst_tflops": burst, "sustained_tflops": sustained, "sustained_clocks": clocks,
+            "fp32_equivalent_burst": burst / 3.0, "fp32_equivalent_sustained": sustained / 3.0,
+            "bf16_over_6_burst": peaks["bf16_tflops"] / 6.0, "bf16_over_6_sustained": peaks["bf16_tflops_sustained"] / 6.0,
+            "how": "torch.matmul (cuBLAS) on FP32 operands with allow_tf32=True: best of 10 single calls, then back to back for 2 s; "
+                   "a third of it is the FP32-equivalent rate of three TF32 products per product; the fractions in this line use "
+                   "the driver-measured BF16 / 6 figures"}
+
+
 def config_records(torch, capi, device, peaks, ffma_tflops) -> dict:
     """The benchmark configurations other than the timed workload, each a few launches on this GPU,
     timed with the reference suite's policy (measure_calls) and, for the short ones, also back to back."""
@@ -1124,6 +1169,15 @@ def main() -> int:
     if not options.no_extras:
         if ffma_tflops is not None:
             line["ffma_probe"] = {"tflops": ffma_tflops, "clocks": ffma_clocks}
+        if not distributed:
+            line["tf32_probe"] = tf32_library_probe(torch, device, peaks)
+            # Beside the official fractions (BF16 / 6): the same values against a third of what the library's own
+            # TF32 GEMM reached on this GPU in this run.
+            if line.get("roofline", {}).get("bound") == "tensor":
+                line["roofline"]["frac_of_library_tf32_over_3"] = line["value"] / line["tf32_probe"]["fp32_equivalent_burst"]
+                if "sustained" in line:
+                    line["sustained"]["frac_of_library_tf32_over_3"] = (line["sustained"]["value"] /
+                                                                         line["tf32_probe"]["fp32_equivalent_sustained"])
         line["plan_reuse"] = {"native": plan_reuse_native(local_rank), "python_ctypes": plan_reuse_overhead(capi, torch, device),
                               "python_torch_gemm": torch_gemm_overhead(ft_torch, torch, device)}
         if not distributed:
