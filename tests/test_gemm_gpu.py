@@ -547,6 +547,46 @@ def test_seeded_random_shapes_layouts_and_scalars_every_family(capi, gpu, oracle
     assert all(count >= 5 for count in ran.values()), ran
 
 
+def test_random_problems_through_the_plan_api_with_the_finders_choice(capi, gpu, oracle):
+    """Two hundred seeded random problems through the staged API, primitive 0 as the Finder ranks it -- the
+    seeded test above forces every family; this one walks the selection rules: few rows, mid-size shapes
+    that take the cluster form or split-K, small outputs, arbitrary extents, A and B plain or as
+    transposed views. Blocked sums are held to the float64 bar, a strictly sequential exact sum
+    (the reference's arithmetic) over more than a hundred K values to the reference's own tolerance."""
+    import random
+
+    rng = random.Random(0)
+    torch.manual_seed(1)
+    chosen = {}
+    for case in range(200):
+        kind = rng.random()
+        if kind < 0.3:
+            m = rng.choice([1, 2, 5, 8, 9, 12, 16, 17, 31, 32, 33, 48, 64])
+            k = rng.choice([256, 512, 1000, 1024, 2048, 4096, 8192])
+            n = rng.choice([128, 192, 500, 1024, 2048, 4096])
+        elif kind < 0.7:
+            m, k, n = rng.randint(65, 1100), rng.choice([128, 300, 512, 1000, 2048, 3072, 4096, 5000]), rng.randint(128, 2400)
+        else:
+            m, k, n = rng.randint(1, 700), rng.randint(1, 700), rng.randint(1, 700)
+        a = torch.randn(k, m, device="cuda").t() if rng.random() < 0.3 else torch.randn(m, k, device="cuda")
+        b = torch.randn(n, k, device="cuda").t() if rng.random() < 0.3 else torch.randn(k, n, device="cuda")
+        c = torch.randn(m, n, device="cuda") if rng.random() < 0.5 else None
+        alpha, beta = (1.0, 0.0) if c is None else (rng.uniform(-2, 2), rng.uniform(-2, 2))
+        d, names = gpu.gemm(a, b, c, alpha, beta)
+        chosen[names[0]] = chosen.get(names[0], 0) + 1
+        what = f"case {case}: {names[0]} {m}x{k}x{n} a plain={a.is_contiguous()} b plain={b.is_contiguous()} alpha={alpha:.3f} beta={beta:.3f}"
+        if names[0] == "Fp32Gemm" and k > 100:
+            exact = alpha * (a.double() @ b.double()) + (beta * c.double() if c is not None else 0.0)
+            slack = 2e-5 * max(1.0, (k / 257.0) ** 0.5)
+            scale = (a.double().abs() @ b.double().abs()) * abs(alpha) + (abs(beta) * c.double().abs() if c is not None else 0.0)
+            assert ((d.double() - exact).abs() <= slack * (1.0 + scale)).all(), what
+        else:
+            check_against_float64(oracle, d, a.contiguous(), b.contiguous(), c, alpha, beta, what)
+    # The draw reaches every family the Finder ranks first somewhere.
+    for name in ("Fp32Gemm", "Fp32GemmSkinny", "Fp32Gemm3xTf32", "Fp32Gemm3xTf32SplitK", "Fp32Gemm3xTf32FewRows"):
+        assert chosen.get(name, 0) >= 3, chosen
+
+
 @pytest.mark.parametrize("m,k,n,ranks", [
     (256, 3072, 384, 6),     # 4 tiles, six K slices
     (384, 1024, 1152, 4),    # 18 tiles
