@@ -87,11 +87,12 @@ std::vector<std::string> B200Heuristic::findCandidates(const GemmProblem& proble
     // tiles -- many CTAs, a short K loop each -- in about 6 to 10 us of device time, where the tensor
     // kernel's pipeline set-up and cluster exchange cost over 20 (256^3: 10.3 against 22.2 us). The
     // condition mirrors the one under which the platform picks that tiling; up to about 48 M
-    // multiply-adds the exact kernel stays ahead (at 512^3 the two are level).
+    // multiply-adds -- 80 M when K is at most 512: 384 x 512 x 384 runs in 14.4 against 18.4 us -- the
+    // exact kernel stays ahead (512^3: 24.6 against 18.0; 256 x 1024 x 256: 22.6 against 16.0).
     const std::uint64_t tiles64 = ceilDiv(shape.m, 64) * ceilDiv(shape.n, 64);
     const std::uint64_t tiles32 = ceilDiv(shape.m, 32) * ceilDiv(shape.n, 32);
     if (shape.m >= 33 && (shape.k <= 512 || (shape.k <= 1024 && tiles32 >= 32)) && tiles64 * 4 <= sm_count &&
-        tiles32 <= 2 * sm_count && shape.m * shape.n * shape.k <= (48ULL << 20)) {
+        tiles32 <= 2 * sm_count && shape.m * shape.n * shape.k <= ((shape.k <= 512 ? 80ULL : 48ULL) << 20)) {
         if (shape.n >= 128 && shape.k >= 256) { return {simt, tensor}; }
         return {simt};
     }

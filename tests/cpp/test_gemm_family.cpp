@@ -269,7 +269,9 @@ TEST(finder_regime_map) {
     // Small outputs with a short K: the exact kernel's 32 x 32 tiling comes first, the tensor kernel behind it.
     CHECK(first(256, 256, 256) == (Names{"Fp32Gemm", "Fp32Gemm3xTf32"}));
     CHECK(first(384, 256, 320) == (Names{"Fp32Gemm", "Fp32Gemm3xTf32"}));
+    CHECK(first(384, 512, 384).front() == "Fp32Gemm");  // 72 M multiply-adds, K = 512: still the exact kernel
     CHECK(first(512, 512, 512).front() != "Fp32Gemm");
+    CHECK(first(256, 1024, 256).front() != "Fp32Gemm");  // 64 M with K = 1024: the tensor kernel
     CHECK(first(17, 1024, 1024).front() == "Fp32GemmSkinny");
     CHECK(first(17, 2048, 512).front() == "Fp32Gemm3xTf32FewRows");
     CHECK(first(64, 1024, 1024).front() == "Fp32Gemm3xTf32FewRows");
