@@ -141,12 +141,9 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             abort_flag = 1;
             healthy    = false;
         }
-        // A timed-out wait is reported and the tile abandoned, by every thread
-        // together: __syncthreads_or makes the decision uniform.
-        if (__syncthreads_or(healthy ? 0 : 1)) {
-            healthy = false;
-            break;
-        }
+        // A thread whose wait ran out has raised the CTA's flag; it multiplies what the stage holds all
+        // the same and every thread reads the flag behind the barrier that ends the block, where the
+        // tile is abandoned by all of them together: one block-wide barrier per K block.
         const unsigned char* a_tile = ring + s * kStageBytes;
         const unsigned char* b_tile = a_tile + kTileBytes;
 #pragma unroll
@@ -218,6 +215,10 @@ simtGemmTma(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // This thread's reads of the stage (generic proxy) before its refill by TMA (async proxy).
         fenceProxyAsync();
         __syncthreads();
+        if (*static_cast<volatile int*>(&abort_flag) != 0) {
+            healthy = false;
+            break;
+        }
     }
     if (!healthy) {
         // Give up on the tile: report, then let the copies that are still in
